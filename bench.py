@@ -1,0 +1,435 @@
+"""Benchmark: BERT-base fp16, batch 1, sequence 128, one CUDA graph per forward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line.
+
+* ``value`` / ``ms_per_step``: latency of one graph replay with the inputs already
+  in device memory, per-step CUDA events, L2 flushed (a 256 MiB write) between
+  steps, mean over exactly K steps, max over ranks.
+* ``e2e``: the same forward through the public call ``compiled(*host_inputs)``:
+  pinned host inputs are copied in, the graph replayed, the result copied back
+  to pinned host memory, host wall clock around each step (device drained at the
+  end of every step).
+* ``roofline``: the largest fused-kernel microbenchmark (bias+GELU+residual over
+  [32*128, 3072] fp16), timed live as a CUDA graph of launches over rotating
+  buffer sets totalling more than four times L2; ``fused_kernels`` lists all nine
+  microbenchmark shapes, ``in_model`` the per-family device time inside the BERT
+  step (those run out of L2 and are launch-bound at batch 1).
+* ``cpu_baseline``: the CPU oracle (a port of the reference's torch backend)
+  timed on this host's cores on the same workload.
+* ``replica_throughput``: batch 32 split over the ranks (32/N per GPU), no
+  collectives, sequences per second summed over ranks.
+
+With N > 1 (torchrun) every rank runs an independent replica; there is no
+data-path collective, only a barrier and a max/sum of the timings.
+``--impl reference`` times the CPU oracle alone on rank 0 (the reference's own
+GPU path is Triton, which this repository does not carry).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / "gpurun_out" / "mlc_cache"))
+
+import torch  # noqa: E402
+
+WORKLOAD = "bert-base fp16 b1 s128, one CUDA graph per forward"
+METRIC = "bert_base_fp16_b1_s128_latency"
+
+
+def _peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs.
+    Read-only: no setting of the GPU is touched."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks",
+               0x100: "display_clocks"}
+
+    def __init__(self, index: int, period: float = 0.02):
+        self.index, self.period = index, period
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------
+# pieces
+# --------------------------------------------------------------------------
+
+def _compiled(name: str, batch: int, dtype, dev, **cfg):
+    from mlc_compiler_b200 import Config, models
+    from mlc_compiler_b200.executor import CompiledModel
+    from mlc_compiler_b200.frontend import load_schedule
+
+    sched = load_schedule(models.schedule_name(name, batch, dtype))
+    model, inputs = models.build(name, batch, dtype=dtype)
+    return CompiledModel(sched, model, Config(**cfg), dev), inputs, sched
+
+
+class L2Flush:
+    def __init__(self, dev, mib: int = 256):
+        self.buf = torch.empty(mib << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def time_replays(cm, dev_inputs, steps: int, warmup: int, flush) -> list[float]:
+    """Per-step device time of one replay, inputs resident, L2 flushed between."""
+    cm(*dev_inputs)
+    for _ in range(warmup):
+        flush()
+        cm.replay()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush()
+        starts[i].record()
+        cm.replay()
+        ends[i].record()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+
+def time_end_to_end(cm, host_inputs, steps: int, warmup: int, flush) -> tuple[list[float], int, int]:
+    """Host wall clock of copy-in, replay, copy-out, per step."""
+    pinned = [t.contiguous().pin_memory() for t in host_inputs]
+    out = cm(*pinned)
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in pinned)
+    d2h = host_out.numel() * host_out.element_size()
+    times = []
+    for i in range(warmup + steps):
+        flush()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = cm(*pinned)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        if i >= warmup:
+            times.append((t1 - t0) * 1e3)
+    return times, h2d, d2h
+
+
+def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64) -> list[dict]:
+    """Each fused-kernel microbenchmark as a CUDA graph of ``launches`` launches
+    cycling over buffer sets whose total size exceeds 4x L2, so every launch
+    reads and writes HBM."""
+    from mlc_compiler_b200 import Config, models
+    from mlc_compiler_b200.frontend import load_schedule
+    from mlc_compiler_b200.runtime import CudaRuntime
+
+    l2 = 126 << 20
+    rows = []
+    for name in ("micro-layernorm", "micro-softmax", "micro-gelu"):
+        for b in batches:
+            sched = load_schedule(models.schedule_name(name, b, torch.float16))
+            k = sched.generated()[0]
+            rt = CudaRuntime(sched, Config(), dev)
+            spec = rt.generated.launch[k.name]
+            model, inputs = models.build(name, b, dtype=torch.float16)
+            table = dict(model.named_parameters())
+            table.update(dict(model.named_buffers()))
+            big = [n for n in set(k.reads()) | set(k.writes()) if n not in sched.params]
+            per_set = sum(sched.buffers[n].nbytes for n in big)
+            sets = max(2, min(4096, -(-4 * l2 // per_set)))
+            n_launch = max(launches, sets)
+            fixed = {n: table[o].detach().to(dev, getattr(torch, sched.buffers[n].dtype))
+                     .contiguous().reshape(-1) for n, o in sched.params.items()
+                     if n in k.reads()}
+            bound = []
+            for s in range(sets):
+                bufs = dict(fixed)
+                for v, t in zip(sched.inputs, inputs):
+                    bufs[v.buffer] = t.to(dev).reshape(-1).clone()
+                for n in big:
+                    if n not in bufs:
+                        bufs[n] = torch.empty(sched.buffers[n].numel, device=dev,
+                                              dtype=getattr(torch, sched.buffers[n].dtype))
+                bound.append(rt.bind(k, bufs)[0])
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for f in bound:
+                    f()
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(n_launch):
+                    bound[i % sets]()
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            reps = 10
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(reps):
+                g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            us = s.elapsed_time(e) * 1e3 / (reps * n_launch)
+            gbs = spec.alg_bytes / us / 1e3
+            rows.append({"kernel": name, "batch": b, "alg_bytes": spec.alg_bytes,
+                         "us_per_launch": round(us, 3), "gbs": round(gbs, 1),
+                         "frac": round(gbs / peak_gbs, 4), "grid": spec.grid, "block": spec.block,
+                         "buffer_sets": sets, "set_bytes": per_set,
+                         "launches_per_graph": n_launch,
+                         "hbm_resident": bool(sets * per_set >= 4 * l2)})
+            del bound, g
+    return rows
+
+
+def in_model_families(cm, dev_inputs, peak_gbs: float) -> list[dict]:
+    """Device time of the generated kernels inside the BERT step, by function."""
+    rows = cm.profile_kernels(dev_inputs, iters=20)
+    table = cm.launch_table
+    agg: dict[str, dict] = {}
+    extern_ms = 0.0
+    for name, summary, ms in rows:
+        if name not in table:
+            extern_ms += ms
+            continue
+        sym = table[name]["symbol"]
+        a = agg.setdefault(sym, {"symbol": sym, "example": summary.split(": ", 1)[1][:60],
+                                 "launches": 0, "ms": 0.0, "alg_bytes": table[name]["alg_bytes"]})
+        a["launches"] += 1
+        a["ms"] += ms
+    out = []
+    for a in sorted(agg.values(), key=lambda r: -r["ms"]):
+        us = a["ms"] * 1e3 / a["launches"]
+        out.append({"symbol": a["symbol"], "example": a["example"], "launches": a["launches"],
+                    "us_per_launch": round(us, 3), "alg_bytes": a["alg_bytes"],
+                    "gbs": round(a["alg_bytes"] / us / 1e3, 1),
+                    "frac": round(a["alg_bytes"] / us / 1e3 / peak_gbs, 4)})
+    out.append({"symbol": "extern (cuBLAS/ATen)", "ms_total": round(extern_ms, 4)})
+    return out
+
+
+def cpu_oracle_times(steps: int, warmup: int) -> tuple[list[float], int, str]:
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import kir_oracle as oracle
+    from mlc_compiler_b200 import models
+    from mlc_compiler_b200.frontend import load_schedule
+
+    sched = load_schedule("bert-base_b1_s128_float16")
+    model, inputs = models.build("bert-base", 1, dtype=torch.float16)
+    table = dict(model.named_parameters())
+    table.update(dict(model.named_buffers()))
+    buffers = oracle.allocate(sched, table, inputs)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.run_schedule(sched, table, inputs, buffers=buffers)
+        if i >= warmup:
+            times.append((time.perf_counter() - t0) * 1e3)
+    return times, torch.get_num_threads(), "whole forwards of the same 200-kernel schedule"
+
+
+# --------------------------------------------------------------------------
+
+def dist_setup(n: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def reduce_scalar(x: float, op: str, world: int, dev) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def run_reference(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
+    steps = min(steps, 60)       # ~0.5 s per forward on 8 cores: stays within a few minutes
+    times, cores, sample = cpu_oracle_times(steps, warmup)
+    ms = statistics.mean(times)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(ms, 4), "unit": "ms",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "device": "cpu",
+                                        "note": "reference torch backend restated (oracle port), "
+                                                "all host threads"},
+        "cpu_baseline": {"value": round(ms, 4), "unit": "ms", "cores": cores, "kind": "port",
+                         "sample": f"{steps} {sample}"},
+        "e2e": {"value": round(ms, 4), "unit": "ms", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_ours(args) -> int:
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the generated kernels have no CPU path")
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = _peaks()
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+
+    cm, host_inputs, sched = _compiled("bert-base", 1, torch.float16, dev)
+    dev_inputs = [t.to(dev) for t in host_inputs]
+    flush = L2Flush(dev)
+    cm(*dev_inputs)
+    torch.cuda.synchronize()
+
+    barrier(world)
+    with ClockSampler(local) as clocks:
+        t_wall = time.perf_counter()
+        per_step = time_replays(cm, dev_inputs, steps, warmup, flush)
+        barrier(world)
+        wall = time.perf_counter() - t_wall
+    ms = reduce_scalar(statistics.mean(per_step), "max", world, dev)
+    med = reduce_scalar(statistics.median(per_step), "max", world, dev)
+
+    e2e_times, h2d, d2h = time_end_to_end(cm, host_inputs, steps, warmup, flush)
+    e2e_ms = reduce_scalar(statistics.mean(e2e_times), "max", world, dev)
+
+    # batch 32 split over the ranks, independent replicas
+    per_gpu = 32 // world
+    tcm, tin, tsched = _compiled("bert-base", per_gpu, torch.float16, dev)
+    tdev = [t.to(dev) for t in tin]
+    tms = statistics.mean(time_replays(tcm, tdev, max(5, steps // 4), 3, flush))
+    seqs = reduce_scalar(per_gpu / (tms / 1e3), "sum", world, dev)
+    slow = reduce_scalar(tms, "max", world, dev)
+
+    line = {
+        "metric": METRIC, "value": round(ms, 5), "unit": "ms", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 5), "median_ms": round(med, 5),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "kernels": len(sched), "generated": cm.generated_launches,
+                   "arena_kib": round(sched.arena_bytes / 1024, 1),
+                   "l2": "flushed between steps (256 MiB write)",
+                   "parallelism": f"{world} independent replicas, no collectives"},
+        "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
+        "gpu_launches": cm.generated_launches * steps,
+        "clocks": clocks.summary(),
+        "timed_region_wall_s": round(wall, 3),
+        "replica_throughput": {"model": "bert-base fp16 s128", "global_batch": per_gpu * world,
+                               "per_gpu_batch": per_gpu, "seq_per_s": round(seqs, 1),
+                               "ms_per_forward": round(slow, 4),
+                               "arena_mb_per_gpu": round(tsched.arena_bytes / 2**20, 2)},
+    }
+
+    if rank == 0:
+        micro = micro_roofline(dev, peak, batches=(1, 8, 32))
+        top = max(micro, key=lambda r: r["alg_bytes"])
+        line["roofline"] = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
+                            "frac": top["frac"], "traffic": None,
+                            "kernel": f"{top['kernel']} b{top['batch']} fp16",
+                            "alg_bytes_per_launch": top["alg_bytes"],
+                            "us_per_launch": top["us_per_launch"], "peak_source": peak_kind}
+        line["fused_kernels"] = micro
+        line["in_model"] = in_model_families(cm, dev_inputs, peak)
+        if world == 1 and not args.no_cpu:
+            times, cores, sample = cpu_oracle_times(10, 1)
+            line["cpu_baseline"] = {"value": round(statistics.mean(times), 3), "unit": "ms",
+                                    "cores": cores, "kind": "port", "sample": f"10 {sample}"}
+    barrier(world)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    return run_reference(args) if args.impl == "reference" else run_ours(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,63 @@
+"""Compiler configuration, field for field the reference's ``Config``
+(``mlc/config.py:14-67``) so that code written against it keeps working, plus
+the few knobs that only the CUDA backend reads.
+
+The pass flags (``elementwise_fusion`` ... ``memory_planning``) are consumed by
+the reference's frontend, which decides *which* kernels exist; this backend reads
+``cuda_graphs``, ``pointwise_block``, ``max_persistent_row`` (already folded into
+``ReductionKernel.two_pass`` upstream, ``mlc/codegen/reduction_lowering.py:258``)
+and ``backend``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from dataclasses import replace as _replace
+
+
+@dataclass
+class Config:
+    # -- passes (read by the frontend) --------------------------------------
+    elementwise_fusion: bool = True
+    recompute: bool = True
+    reduction_fusion: bool = True
+    memory_planning: bool = True
+    cuda_graphs: bool = True
+
+    # -- codegen -------------------------------------------------------------
+    #: upper bound on elements one CTA of a pointwise kernel covers
+    pointwise_block: int = 1024
+    max_persistent_row: int = 16384
+    fp32_accumulate: bool = True
+
+    # -- cost model (read by the frontend) ----------------------------------
+    flops_per_byte: float = 20.0
+    launch_overhead_bytes: float = 4.5e6
+    graph_launch_overhead_bytes: float = 1.1e6
+    max_recompute_ops: int = 32
+
+    # -- misc ------------------------------------------------------------------
+    backend: str = "auto"  # "auto" | "cuda" | "torch"; "triton" is refused
+    debug: bool = False
+
+    # -- CUDA backend only -----------------------------------------------------
+    #: packs of 128 bits each thread of a persistent row reduction aims to own
+    reduction_packs_per_thread: int = 4
+    #: force the number of threads that share one row (0 = choose)
+    reduction_group: int = 0
+    #: launch generated kernels with programmatic stream serialisation and emit
+    #: the matching grid-dependency instructions
+    dependent_launch: bool = False
+
+    @property
+    def effective_launch_bytes(self) -> float:
+        return (self.graph_launch_overhead_bytes if self.cuda_graphs
+                else self.launch_overhead_bytes)
+
+    def replace(self, **kw) -> "Config":
+        return _replace(self, **kw)
+
+
+NO_FUSION = Config(elementwise_fusion=False, recompute=False, reduction_fusion=False,
+                   memory_planning=False, cuda_graphs=False)
+ELEMENTWISE_ONLY = Config(reduction_fusion=False)

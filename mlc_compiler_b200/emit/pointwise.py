@@ -1,0 +1,189 @@
+"""Pointwise kernels: one thread owns one pack of V consecutive flat indices.
+
+Replaces ``emit_pointwise`` (``mlc/codegen/triton_backend.py:206-254``).  Where
+the Triton form is a flat scalar ``idx = pid * BLOCK + arange`` and trusts the
+compiler to find vector accesses, this emitter decides them: V is the number of
+elements of the *narrowest* operand that fill 128 bits, every operand gets the
+widest access its index map proves legal (``indexing.classify``), and the body
+is straight-line code over ``V`` lanes held in registers.  A broadcast operand
+such as a bias row (``idx % 768``) is still one packed load per thread because
+768 is a multiple of V; a gather such as the head-merge copy
+(``(idx / 768) * 64 + ((idx / 64) % 12) * 8192 + idx % 64``) keeps 128-bit
+accesses because every coefficient is a multiple of V.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from .. import kir
+from . import expr as X
+from .indexing import Access, check_bounds, classify, needs_64bit, pow2_ceil, render_offset
+
+
+@dataclass
+class LaunchSpec:
+    """Grid and block of one launch; everything else is baked into the source.
+    Counterpart of the reference's ``LaunchSpec`` (``triton_backend.py:105-112``)."""
+
+    grid: int
+    block: int
+    smem: int = 0
+    #: descriptive, for reports: elements per thread-pack and algorithmic bytes
+    vector: int = 1
+    alg_bytes: int = 0
+
+    def as_dict(self) -> dict:
+        return {"grid": (self.grid,), "block": self.block, "smem": self.smem,
+                "vector": self.vector, "alg_bytes": self.alg_bytes}
+
+
+def algorithmic_bytes(inputs, outputs, iter_numel: int) -> int:
+    """Distinct elements addressed per operand x itemsize (broadcast operands
+    counted once), the figure the roofline report divides by kernel time."""
+    total = 0
+    for a in inputs:
+        total += min(a.index.distinct_elements(), iter_numel) * kir.ITEMSIZE[a.dtype]
+    for a in outputs:
+        total += min(a.index.distinct_elements(), iter_numel) * kir.ITEMSIZE[a.dtype]
+    return total
+
+
+def pick_vector(operands, numel: int, cap_bytes: int = 16) -> int:
+    smallest = min((kir.ITEMSIZE[a.dtype] for a in operands), default=4)
+    v = max(1, cap_bytes // smallest)
+    while v > 1 and numel % v != 0:
+        v //= 2
+    return v
+
+
+def _chunks(acc: Access, v: int):
+    return range(0, v, acc.width)
+
+
+def emit_pointwise(k: kir.PointwiseKernel, cfg, buffers: dict[str, kir.BufferSpec] | None = None,
+                   name: str | None = None) -> tuple[str, LaunchSpec]:
+    name = name or k.name
+    numel = k.numel
+    operands = list(k.inputs) + list(k.outputs)
+    if buffers is not None:
+        for a in operands:
+            check_bounds(a.index, buffers[a.buffer].numel, f"{k.name}:{a.name}")
+
+    V = pick_vector(operands, numel)
+    # narrow V until nothing is forced into per-element access only because the
+    # pack is wider than the operand's contiguous run
+    packs = numel // V
+    extents = [numel] + [a.index.bounds()[1] + 1 for a in operands]
+    it = "i64" if needs_64bit(*extents) else "int"
+
+    block_cap = max(32, pow2_ceil(max(1, int(getattr(cfg, "pointwise_block", 1024))) // V))
+    block = max(32, min(1024, block_cap, pow2_ceil(packs)))
+    grid = (packs + block - 1) // block
+    guard = packs % block != 0
+
+    aliased = {a.buffer for a in k.inputs} & {a.buffer for a in k.outputs}
+    params = []
+    for i, a in enumerate(k.inputs):
+        r = "" if a.buffer in aliased else " __restrict__"
+        params.append(f"const {X.STORAGE_T[a.dtype]}*{r} in{i}")
+    for i, a in enumerate(k.outputs):
+        r = "" if a.buffer in aliased else " __restrict__"
+        params.append(f"{X.STORAGE_T[a.dtype]}*{r} out{i}")
+
+    L: list[str] = []
+    L.append(f'extern "C" __global__ void __launch_bounds__({block}, {max(1, min(16, 512 // block))}) '
+             f'{name}({", ".join(params)}) {{')
+    L.append(f"    // pointwise {list(k.space)} = {numel} elements, {V} per thread, "
+             f"{grid} x {block} threads")
+    L.append("    MLCB_GRID_WAIT();")
+    L.append(f"    const {it} pack = ({it})blockIdx.x * {block} + threadIdx.x;")
+    if guard:
+        L.append(f"    if (pack >= {packs}) return;")
+    L.append(f"    const {it} i0 = pack * {V};")
+
+    names = {"idx": "idx"}
+    at_i0 = {"idx": "i0"}
+    loads: list[X.Val] = []
+    inner: list[str] = []   # per-element loads placed inside the lane loop
+    need_idx = False
+    for i, a in enumerate(k.inputs):
+        acc = classify(a.index, "idx", V)
+        st, rt = X.STORAGE_T[a.dtype], X.REG_T[a.dtype]
+        vdt = X.promoted_load_dtype(a.dtype)
+        if acc.mode == "bcast" and acc.width == V:
+            L.append(f"    const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, at_i0)}));"
+                     f"  // {a.name}")
+            loads.append(X.Val(f"v{i}", vdt))
+        elif acc.mode == "contig" and acc.width == V and V > 1:
+            L.append(f"    {rt} v{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + ({render_offset(a.index, at_i0)}), v{i});"
+                     f"  // {a.name}")
+            loads.append(X.Val(f"v{i}[j]", vdt))
+        elif acc.mode == "contig" and acc.width > 1:
+            L.append(f"    {rt} v{i}[{V}];  // {a.name}: runs of {acc.width}")
+            for c in _chunks(acc, V):
+                off = render_offset(a.index, {"idx": f"(i0 + {c})"})
+                L.append(f"    mlcb_load_at<{st}, {acc.width}, {V}>(in{i} + ({off}), v{i}, {c});")
+            loads.append(X.Val(f"v{i}[j]", vdt))
+        else:
+            need_idx = True
+            inner.append(f"        const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, names)}));"
+                         f"  // {a.name}")
+            loads.append(X.Val(f"v{i}", vdt))
+
+    out_acc = []
+    for i, a in enumerate(k.outputs):
+        acc = classify(a.index, "idx", V)
+        if acc.mode != "contig":
+            acc = Access("contig", 1)
+        out_acc.append(acc)
+        if acc.width > 1:
+            L.append(f"    {X.REG_T[a.dtype]} o{i}[{V}];")
+        else:
+            need_idx = True
+
+    L.append("    MLCB_GRID_TRIGGER();")
+    L.append("#pragma unroll")
+    L.append(f"    for (int j = 0; j < {V}; ++j) {{")
+    if need_idx:
+        L.append(f"        const {it} idx = i0 + j;")
+    L += inner
+    refs: dict[str, X.Val] = {}
+    for temp, e in k.body:
+        v = X.render(e, loads, refs)
+        L.append(f"        const {X.REG_T[v.dtype]} {temp} = {v.code};")
+        refs[temp] = X.Val(temp, v.dtype, v.dim)
+    for i, a in enumerate(k.outputs):
+        v = X.render(k.out_expr[a.name], loads, refs)
+        code = store_code(v, a.dtype)
+        if out_acc[i].width > 1:
+            L.append(f"        o{i}[j] = {code};  // {a.name}")
+        else:
+            L.append(f"        mlcb_store1<{X.STORAGE_T[a.dtype]}>(out{i} + ({render_offset(a.index, names)}), {code});"
+                     f"  // {a.name}")
+    L.append("    }")
+    for i, a in enumerate(k.outputs):
+        acc = out_acc[i]
+        st = X.STORAGE_T[a.dtype]
+        if acc.width == V and V > 1:
+            L.append(f"    mlcb_store<{st}, {V}>(out{i} + ({render_offset(a.index, at_i0)}), o{i});")
+        elif acc.width > 1:
+            for c in _chunks(acc, V):
+                off = render_offset(a.index, {"idx": f"(i0 + {c})"})
+                L.append(f"    mlcb_store_at<{st}, {acc.width}, {V}>(out{i} + ({off}), o{i}, {c});")
+    L.append("}")
+
+    spec = LaunchSpec(grid=grid, block=block, vector=V,
+                      alg_bytes=algorithmic_bytes(k.inputs, k.outputs, numel))
+    return "\n".join(L), spec
+
+
+def store_code(v: X.Val, out_dtype: str) -> str:
+    """Register value handed to a store of ``out_dtype``.  The store itself
+    rounds a float register to fp16/bf16, so a float32 (or already narrow)
+    value is passed through rather than rounded twice."""
+    if out_dtype in kir.NARROW_FLOATS and v.dtype in ("float32", out_dtype):
+        return v.code
+    if out_dtype in kir.NARROW_FLOATS:
+        return X.convert(v.code, v.dtype, "float32")
+    return X.convert(v.code, v.dtype, out_dtype)

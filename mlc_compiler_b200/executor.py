@@ -1,0 +1,382 @@
+"""Executor: bind buffers, resolve the launch plan, capture it as a CUDA graph.
+
+Same behaviour as the reference's ``CompiledModel``
+(``mlc/runtime/executor.py:41-366``) over this package's schedule IR, for hosts
+that load a serialised schedule instead of running the reference frontend:
+
+* every buffer is a flat 1-D tensor; planned intermediates are 256-byte aligned
+  slices of one ``uint8`` arena (``:119-130``), parameters are uploaded and
+  flattened once (``:52-56``), inputs are copied into fixed buffers so every
+  pointer is stable for the life of the model (``:132-156``);
+* the launch plan is resolved once (``:165-184``); extern kernels go to the ATen
+  ``.out`` overload so cuBLAS writes straight into the arena (``:369-438``);
+* with ``cfg.cuda_graphs`` the plan is warmed up three times on a side stream,
+  captured, and replayed per call (``:269-307``); outputs alias storage the next
+  call overwrites (``:244-251``).
+
+Generated kernels only ever run through the C ABI on a CUDA device.  There is
+no interpreter fallback in this class.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Mapping, Sequence
+
+import torch
+
+from . import kir
+from .config import Config
+from .runtime import BackendError, CudaRuntime, LaunchRun
+
+
+class ExecutionError(Exception):
+    pass
+
+
+def select_backend(cfg, device: torch.device) -> str:
+    """``"auto"`` means the CUDA backend and requires a CUDA device; a CUDA
+    compile never degrades to an interpreter (contrast the reference's silent
+    fallback at ``mlc/runtime/executor.py:36-37``)."""
+    b = getattr(cfg, "backend", "auto")
+    if b == "triton":
+        raise ValueError("the Triton backend has been removed; use backend='auto' or 'cuda'")
+    if b == "torch":
+        raise BackendError("backend='torch' is the reference's interpreter; this executor "
+                           "only runs generated CUDA kernels")
+    if b not in ("auto", "cuda"):
+        raise ValueError(f"unknown backend {b!r}")
+    if device.type != "cuda":
+        raise BackendError(f"the CUDA backend needs a CUDA device, got {device}")
+    return "cuda"
+
+
+# --------------------------------------------------------------------------
+# extern dispatch
+# --------------------------------------------------------------------------
+
+def resolve_op(op: str):
+    """``"aten.mm.default"`` -> the OpOverload."""
+    parts = op.split(".")
+    if len(parts) < 2:
+        raise ExecutionError(f"{op} has no dispatch target")
+    packet = getattr(getattr(torch.ops, parts[0]), parts[1])
+    return getattr(packet, parts[2] if len(parts) > 2 else "default")
+
+
+def out_variant(op: str):
+    """The ``.out`` overload when it takes the same arguments plus ``out``;
+    decided from the schema, never by trying the call
+    (``mlc/runtime/executor.py:405-438``)."""
+    parts = op.split(".")
+    if parts[0] != "aten":
+        return None
+    target = resolve_op(op)
+    packet = getattr(torch.ops.aten, parts[1])
+    cand = getattr(packet, "out", None)
+    if cand is None:
+        return None
+    try:
+        want = [a.name for a in target._schema.arguments]
+        have = [a.name for a in cand._schema.arguments]
+    except AttributeError:
+        return None
+    return cand if have[:len(want)] == want and have[len(want):] == ["out"] else None
+
+
+def _materialise(a, buffers):
+    if isinstance(a, kir.View):
+        return a.as_torch(buffers[a.buffer])
+    if isinstance(a, (list, tuple)):
+        return type(a)(_materialise(x, buffers) for x in a)
+    if isinstance(a, dict) and "dtype" in a:
+        return kir.torch_dtype(a["dtype"])
+    return a
+
+
+def bind_extern(k: kir.ExternKernel, buffers: dict[str, torch.Tensor]):
+    """Resolve operands against the fixed buffer table; never executes the op."""
+    target = resolve_op(k.op)
+    args = [_materialise(a, buffers) for a in k.args]
+    kwargs = {n: _materialise(a, buffers) for n, a in k.kwargs.items()}
+    variant = out_variant(k.op) if len(k.outputs) == 1 else None
+    dest = k.outputs[0].as_torch(buffers[k.outputs[0].buffer]) if variant is not None else None
+    outs = [buffers[o.buffer] for o in k.outputs]
+    return [target, variant, args, kwargs, dest, outs]
+
+
+def run_bound_extern(bound) -> None:
+    target, variant, args, kwargs, dest, outs = bound
+    if variant is not None:
+        variant(*args, **kwargs, out=dest)
+        return
+    result = target(*args, **kwargs)
+    results = result if isinstance(result, (list, tuple)) else [result]
+    for buf, r in zip(outs, results):
+        buf.copy_(r.contiguous().reshape(-1))
+
+
+# --------------------------------------------------------------------------
+
+class CompiledModel:
+    """A schedule bound to a device, callable like the module it came from."""
+
+    def __init__(self, schedule: kir.Schedule, params: Mapping[str, torch.Tensor] | torch.nn.Module,
+                 cfg: Config | None = None, device: str | torch.device = "cuda") -> None:
+        self.schedule = schedule
+        self.cfg = cfg or Config()
+        self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.backend = select_backend(self.cfg, self.device)
+
+        self._live = schedule.live_buffers()
+        self.params: dict[str, torch.Tensor] = {}
+        source = _tensor_table(params)
+        for buf, origin in schedule.params.items():
+            if buf not in self._live:
+                continue
+            t = source.get(origin)
+            if t is None:
+                t = source.get(buf)
+            if t is None:
+                raise ExecutionError(f"no tensor supplied for parameter {buf} ({origin})")
+            spec = schedule.buffers[buf]
+            if t.numel() != spec.numel:
+                raise ExecutionError(f"parameter {origin}: schedule wants {spec.shape}, "
+                                     f"got {tuple(t.shape)}")
+            self.params[buf] = (t.detach().to(self.device, kir.torch_dtype(spec.dtype))
+                                .contiguous().reshape(-1))
+
+        self._module = CudaRuntime(schedule, self.cfg, self.device)
+        self._arena: torch.Tensor | None = None
+        self._resident: dict[str, torch.Tensor] | None = None
+        self._plan: list | None = None
+        self._static_inputs: list[torch.Tensor] | None = None
+        self._graph_replay = None
+        self._static_outputs: Any = None
+        #: generated-kernel launches per forward (what a bench reports)
+        self.generated_launches = len(schedule.generated())
+
+    # -- allocation ------------------------------------------------------------
+    def _check_inputs(self, inputs: Sequence[torch.Tensor]) -> None:
+        want = self.schedule.inputs
+        if len(inputs) != len(want):
+            raise ExecutionError(f"expected {len(want)} inputs, got {len(inputs)}")
+        for v, t in zip(want, inputs):
+            if tuple(t.shape) != tuple(v.shape):
+                raise ExecutionError(
+                    f"input {v.name}: compiled for {tuple(v.shape)}, called with {tuple(t.shape)}")
+
+    def _empty(self, spec: kir.BufferSpec) -> torch.Tensor:
+        return torch.empty(spec.numel, dtype=kir.torch_dtype(spec.dtype), device=self.device)
+
+    def _get_arena(self) -> torch.Tensor:
+        need = max(self.schedule.arena_bytes, 1)
+        if self._arena is None or self._arena.numel() < need:
+            self._arena = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._arena
+
+    def _resident_buffers(self, inputs: Sequence[torch.Tensor]) -> dict[str, torch.Tensor]:
+        self._check_inputs(inputs)
+        if self._resident is None:
+            sch = self.schedule
+            buffers = dict(self.params)
+            for b in sch.buffers.values():
+                if b.name in buffers or b.plannable or b.name not in self._live:
+                    continue
+                buffers[b.name] = self._empty(b)
+            offsets = sch.plan.offsets if sch.plan.mode == "arena" else {}
+            arena = self._get_arena()
+            for b in sch.buffers.values():
+                if b.name in buffers or b.name not in self._live:
+                    continue
+                off = offsets.get(b.name)
+                if off is None:
+                    buffers[b.name] = self._empty(b)
+                else:
+                    buffers[b.name] = arena[off:off + b.nbytes].view(kir.torch_dtype(b.dtype))
+            self._resident = buffers
+            self._static_inputs = [buffers[v.buffer] for v in sch.inputs]
+        for dst, t in zip(self._static_inputs, inputs):
+            dst.copy_(t.reshape(-1), non_blocking=True)
+        return self._resident
+
+    # -- execution -------------------------------------------------------------
+    def _build_plan(self, buffers: dict[str, torch.Tensor]) -> list:
+        """("extern", bound) and ("cuda", LaunchRun) entries; consecutive
+        generated kernels share one crossing of the C boundary."""
+        plan: list = []
+        run: list = []
+        self._bound: dict[str, Any] = {}
+
+        def flush():
+            if run:
+                plan.append(("cuda", LaunchRun(self._module.lib, list(run))))
+                run.clear()
+
+        for k in self.schedule.kernels:
+            if isinstance(k, kir.ExternKernel):
+                flush()
+                b = bind_extern(k, buffers)
+                self._bound[k.name] = ("extern", b)
+                plan.append(("extern", b))
+            elif isinstance(k, (kir.PointwiseKernel, kir.ReductionKernel)):
+                fn = self._module.bind(k, buffers)[0]
+                self._bound[k.name] = ("cuda", fn)
+                run.append(fn)
+            else:
+                raise ExecutionError(f"cannot execute {type(k).__name__}")
+        flush()
+        return plan
+
+    def run_kernels(self, buffers: dict[str, torch.Tensor] | None = None) -> None:
+        if self._plan is None:
+            raise ExecutionError("no launch plan: call the model (or forward) once first")
+        for kind, payload in self._plan:
+            if kind == "cuda":
+                payload()
+            else:
+                run_bound_extern(payload)
+
+    def run_one(self, k, buffers: dict[str, torch.Tensor]) -> None:
+        if isinstance(k, kir.ExternKernel):
+            run_bound_extern(bind_extern(k, buffers))
+        elif isinstance(k, (kir.PointwiseKernel, kir.ReductionKernel)):
+            self._module.launch(k, buffers)
+        else:
+            raise ExecutionError(f"cannot execute {type(k).__name__}")
+
+    def _run_eager(self, inputs) -> dict[str, torch.Tensor]:
+        """The unplanned baseline: allocate each intermediate when it is first
+        written, drop it after its last read (``executor.py:216-228``)."""
+        self._check_inputs(inputs)
+        sch, plan = self.schedule, self.schedule.plan
+        buffers = dict(self.params)
+        for v, t in zip(sch.inputs, inputs):
+            spec = sch.buffers[v.buffer]
+            buffers[v.buffer] = (t.to(self.device, kir.torch_dtype(spec.dtype))
+                                 .contiguous().reshape(-1))
+        for b in sch.buffers.values():
+            if b.name not in buffers and not b.plannable and b.name in self._live:
+                buffers[b.name] = self._empty(b)
+        for i, k in enumerate(sch.kernels):
+            for name in plan.alloc_at.get(i, ()):
+                if name in self._live:
+                    buffers[name] = self._empty(sch.buffers[name])
+            self.run_one(k, buffers)
+            for name in plan.free_at.get(i, ()):
+                buffers.pop(name, None)
+        return buffers
+
+    def forward(self, *inputs: torch.Tensor):
+        if self.schedule.plan.mode == "eager":
+            return self._collect(self._run_eager(inputs))
+        buffers = self._resident_buffers(inputs)
+        if self._plan is None:
+            self._plan = self._build_plan(buffers)
+        self.run_kernels(buffers)
+        return self._collect(buffers)
+
+    def _collect(self, buffers: dict[str, torch.Tensor]):
+        outs = [v.as_torch(buffers[v.buffer]) for v in self.schedule.outputs]
+        return outs[0] if len(outs) == 1 else tuple(outs)
+
+    def __call__(self, *inputs: torch.Tensor):
+        if self.cfg.cuda_graphs and self.schedule.plan.mode == "arena":
+            return self._call_captured(inputs)
+        return self.forward(*inputs)
+
+    # -- CUDA graphs -------------------------------------------------------------
+    def _call_captured(self, inputs):
+        if self._graph_replay is None:
+            self._capture(inputs)
+        else:
+            self._check_inputs(inputs)
+        for dst, src in zip(self._static_inputs, inputs):
+            dst.copy_(src.reshape(-1), non_blocking=True)
+        self._graph_replay.replay()
+        return self._static_outputs
+
+    def _capture(self, inputs) -> None:
+        buffers = self._resident_buffers(inputs)
+        if self._plan is None:
+            self._plan = self._build_plan(buffers)
+        # Warm up off the capture stream: cuBLAS picks algorithms and allocates
+        # workspaces on first use, which must not be recorded.
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.run_kernels(buffers)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.run_kernels(buffers)
+        self._graph_replay = g
+        self._static_outputs = self._collect(buffers)
+
+    def replay(self) -> None:
+        """Replay the captured graph on the inputs already resident."""
+        if self._graph_replay is None:
+            raise ExecutionError("nothing captured yet: call the model once")
+        self._graph_replay.replay()
+
+    # -- profiling -----------------------------------------------------------------
+    def profile_kernels(self, inputs, iters: int = 20) -> list[tuple]:
+        """Per-kernel device time over the bound plan, in place
+        (``executor.py:309-352``): (name, summary, milliseconds)."""
+        buffers = self._resident_buffers(inputs)
+        if self._plan is None:
+            self._plan = self._build_plan(buffers)
+        for _ in range(3):
+            self.run_kernels(buffers)
+        torch.cuda.synchronize(self.device)
+
+        def run(entry):
+            kind, payload = entry
+            if kind == "cuda":
+                payload[payload.grid]()
+            else:
+                run_bound_extern(payload)
+
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        out = []
+        for k in self.schedule.kernels:
+            entry = self._bound[k.name]
+            for _ in range(3):
+                run(entry)
+            torch.cuda.synchronize(self.device)
+            start.record()
+            for _ in range(iters):
+                run(entry)
+            end.record()
+            end.synchronize()
+            out.append((k.name, k.summary(), start.elapsed_time(end) / iters))
+        return out
+
+    # -- introspection -------------------------------------------------------------
+    def source(self) -> str:
+        return self._module.source
+
+    def source_path(self):
+        return self._module.path
+
+    def kernel_source(self, name: str) -> str:
+        return self._module.generated.kernel_source(name)
+
+    @property
+    def launch_table(self) -> dict:
+        return self._module.launch_table
+
+    def __repr__(self) -> str:  # pragma: no cover
+        return (f"CompiledModel({self.schedule.name}, {len(self.schedule)} kernels, "
+                f"backend={self.backend}, device={self.device})")
+
+
+def _tensor_table(params) -> dict[str, torch.Tensor]:
+    if isinstance(params, torch.nn.Module):
+        table = dict(params.named_parameters())
+        table.update(dict(params.named_buffers()))
+        return table
+    return dict(params)

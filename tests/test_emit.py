@@ -1,0 +1,143 @@
+"""The CUDA emitter, checked without a GPU: every generated module must compile
+for sm_100a, cover every kernel, take one pointer per operand, be deterministic,
+and use packed accesses where the index maps allow them."""
+
+import re
+import shutil
+
+import pytest
+
+from conftest import load_tiny, tiny_cases
+from mlc_compiler_b200 import Config, kir
+from mlc_compiler_b200 import build as B
+from mlc_compiler_b200.emit import generate_module
+from mlc_compiler_b200.emit.indexing import classify
+from mlc_compiler_b200.frontend import load_schedule
+
+needs_nvcc = pytest.mark.skipif(shutil.which("nvcc") is None and B.nvcc_path() is None,
+                                reason="nvcc not installed")
+
+COMPILE_CASES = [s for s in tiny_cases()
+                 if s.endswith(("__default__float32", "__streamed__float32", "__default__float16",
+                                "__streamed__bfloat16", "__no_fusion__float32"))
+                 and not s.startswith("block_b8")]
+
+
+def _signature(src: str, symbol: str) -> list[str]:
+    m = re.search(rf"{symbol}\((.*?)\) \{{", src, re.S)
+    return [p for p in m.group(1).split(",") if p.strip()]
+
+
+@pytest.mark.parametrize("stem", tiny_cases())
+def test_launch_table_covers_every_generated_kernel(stem):
+    s = load_tiny(stem)["schedule"]
+    mod = generate_module(s, Config())
+    gen = [k.name for k in s.generated()]
+    assert sorted(mod.launch) == sorted(gen)
+    for k in s.generated():
+        sym = mod.symbol[k.name]
+        assert f'extern "C" __global__' in mod.kernel_source(k.name)
+        assert len(_signature(mod.source, sym)) == len(k.inputs) + len(k.outputs)
+        spec = mod.launch[k.name]
+        assert spec.grid >= 1 and 32 <= spec.block <= 1024
+
+
+def test_generation_is_deterministic():
+    s = load_schedule("bert-base_b1_s128_float16")
+    assert generate_module(s, Config()).source == generate_module(s, Config()).source
+
+
+def test_identical_layers_share_one_function():
+    s = load_schedule("bert-base_b1_s128_float16")
+    mod = generate_module(s, Config())
+    assert len(mod.launch) == 100
+    assert len(set(mod.symbol.values())) <= 12
+
+
+def test_multiply_by_one_never_reaches_the_source():
+    s = load_schedule("bert-base_b1_s128_float16")
+    src = generate_module(s, Config()).source
+    assert "* (0x1.0000000000000p+0f)" not in src
+
+
+def test_bias_add_is_fully_packed():
+    """[128,768] + bias[768] in fp16: one 128-bit load per operand, no tail guard."""
+    s = load_schedule("bert-base_b1_s128_float16")
+    k = s.kernel("k7")
+    text = generate_module(s, Config()).kernel_source("k7")
+    assert text.count("mlcb_load<__half, 8>") == 2
+    assert "mlcb_store<__half, 8>" in text
+    assert "if (pack >=" not in text
+    assert classify(k.inputs[1].index, "idx", 8).width == 8
+
+
+def test_head_merge_copy_keeps_wide_accesses():
+    s = load_schedule("bert-base_b1_s128_float16")
+    text = generate_module(s, Config()).kernel_source("k15")
+    assert "mlcb_load<__half, 8>" in text and "mlcb_load1" not in text
+
+
+def test_broadcast_and_gather_classification():
+    bias = kir.IndexMap((kir.Axis("idx", 98304, ((768, 1, 1),)),))
+    assert classify(bias, "idx", 8).mode == "contig"
+    per_row = kir.IndexMap((kir.Axis("idx", 98304, ((128, 768, 1),)),))
+    a = classify(per_row, "idx", 8)
+    assert (a.mode, a.width) == ("bcast", 8)
+    transposed = kir.IndexMap((kir.Axis("idx", 8192, ((64, 128, 1), (128, 1, 64))),))
+    assert classify(transposed, "idx", 8).width == 1
+    odd_base = kir.IndexMap((kir.Axis("idx", 64, ((64, 1, 1),)),), base=4)
+    assert classify(odd_base, "idx", 8).width == 4
+
+
+def test_reductions_accumulate_in_fp32_and_store_narrow():
+    s = load_schedule("micro-layernorm_b1_s128_float16")
+    text = generate_module(s, Config()).source
+    assert "float acc_" in text
+    assert "mlcb_store<__half, 8>" in text
+    assert "mlcb_load<__half, 8>" in text
+
+
+def test_out_of_range_index_map_is_refused_at_emit_time():
+    s = load_tiny("pointwise__default__float32")["schedule"]
+    k = s.generated()[0]
+    bad = kir.IndexMap(k.inputs[0].index.axes, base=1)
+    k.inputs[0] = kir.Operand(k.inputs[0].name, k.inputs[0].buffer, k.inputs[0].dtype, bad)
+    with pytest.raises(ValueError, match="outside a buffer"):
+        generate_module(s, Config())
+
+
+def test_unknown_function_raises_key_error():
+    s = load_tiny("pointwise__default__float32")["schedule"]
+    k = s.generated()[0]
+    k.body.append(("tz", kir.Call("bessel", (kir.Load(0),))))
+    with pytest.raises(KeyError):
+        generate_module(s, Config())
+
+
+@needs_nvcc
+@pytest.mark.parametrize("stem", COMPILE_CASES)
+def test_tiny_modules_compile_for_sm_100a(stem, tmp_path):
+    s = load_tiny(stem)["schedule"]
+    if not s.generated():
+        pytest.skip("no generated kernels")
+    src = generate_module(s, Config()).source
+    log = B.nvcc_cubin(src, tmp_path / "m.cubin", verbose=True)
+    assert "error" not in log.lower()
+    assert " bytes spill stores" in log and not re.search(r"[1-9]\d* bytes spill stores", log)
+
+
+@needs_nvcc
+@pytest.mark.parametrize("name", ["bert-base_b1_s128_float16", "gpt2-small_b8_s128_bfloat16",
+                                  "micro-gelu_b32_s128_float16", "micro-softmax_b8_s128_float16"])
+def test_benchmark_modules_compile_for_sm_100a(name, tmp_path):
+    src = generate_module(load_schedule(name), Config()).source
+    log = B.nvcc_cubin(src, tmp_path / "m.cubin", verbose=True)
+    assert not re.search(r"[1-9]\d* bytes spill stores", log)
+
+
+@needs_nvcc
+def test_dependent_launch_variant_compiles(tmp_path):
+    src = generate_module(load_schedule("bert-base_b1_s128_float16"),
+                          Config(dependent_launch=True)).source
+    assert "#define MLCB_PDL 1" in src
+    B.nvcc_cubin(src, tmp_path / "m.cubin")

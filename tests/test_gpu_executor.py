@@ -1,0 +1,131 @@
+"""Executor contracts on a CUDA device: arena isolation, input checking, output
+aliasing, CUDA-graph replay, per-kernel profiling, launches through the C ABI."""
+
+import pytest
+import torch
+
+from conftest import assert_close, load_tiny
+from mlc_compiler_b200 import Config, kir
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda", 0)
+
+
+def _model(stem, dev, **cfg):
+    from mlc_compiler_b200.executor import CompiledModel
+
+    d = load_tiny(stem)
+    return d, CompiledModel(d["schedule"], d["params"], Config(**cfg), dev)
+
+
+def test_wrong_shape_is_refused_with_the_reference_message(dev):
+    from mlc_compiler_b200.executor import ExecutionError
+
+    d, cm = _model("block__default__float32", dev)
+    x = d["inputs"][0].to(dev)
+    cm(x)
+    with pytest.raises(ExecutionError, match="compiled for"):
+        cm(x[:, :4])
+    with pytest.raises(ExecutionError, match="expected 1 inputs"):
+        cm(x, x)
+
+
+def test_outputs_alias_static_storage_and_inputs_are_copied(dev):
+    d, cm = _model("block__default__float32", dev)
+    x = d["inputs"][0].to(dev)
+    a = cm(x)
+    first = a.clone()
+    b = cm(x * 2.0)
+    assert a.data_ptr() == b.data_ptr()          # same storage, overwritten by the next call
+    assert not torch.equal(first, b)
+    x2 = x.clone()
+    c = cm(x2).clone()
+    x2.zero_()                                   # caller's tensor is not aliased by the model
+    torch.cuda.synchronize()
+    assert_close(cm(x).clone(), first, "float32", "replay after other inputs")
+    assert_close(c, first, "float32", "copy of inputs")
+
+
+def test_kernels_never_write_outside_their_arena_slices(dev):
+    """Canaries between planned buffers: pad the arena, fill the padding with a
+    pattern, run, and check that only planned byte ranges changed."""
+    from mlc_compiler_b200.executor import CompiledModel
+
+    d = load_tiny("block__default__float32")
+    s = d["schedule"]
+    pad = 256
+    shifted = kir.loads(kir.dumps(s))
+    order = sorted(shifted.plan.offsets, key=lambda n: shifted.plan.offsets[n])
+    # re-pack with a guard band after every buffer, keeping relative order
+    live_end = {}
+    for n in order:
+        shifted.plan.offsets[n] = s.plan.offsets[n] * 2 + pad
+        live_end[n] = shifted.plan.offsets[n] + s.buffers[n].nbytes
+    shifted.plan.arena_bytes = s.plan.arena_bytes * 2 + 2 * pad + 4096
+    cm = CompiledModel(shifted, d["params"], Config(cuda_graphs=False), dev)
+    arena = cm._get_arena()
+    arena.fill_(0xA5)
+    out = cm(d["inputs"][0].to(dev))
+    torch.cuda.synchronize()
+    assert_close(out, d["outputs"][0], "float32", "padded arena output")
+    covered = torch.zeros(arena.numel(), dtype=torch.bool, device=dev)
+    for n in order:
+        covered[shifted.plan.offsets[n]:live_end[n]] = True
+    assert bool((arena[~covered] == 0xA5).all()), "a kernel wrote outside its buffer"
+
+
+def test_graph_and_plain_execution_agree_bitwise(dev):
+    d, plain = _model("block_b8__default__float32", dev, cuda_graphs=False)
+    _, graphed = _model("block_b8__default__float32", dev, cuda_graphs=True)
+    x = d["inputs"][0].to(dev)
+    a = plain(x).clone()
+    graphed(x)
+    b = graphed(x).clone()
+    assert torch.equal(a, b)
+
+
+def test_unplanned_schedule_runs_the_eager_path(dev):
+    d, cm = _model("block__no_fusion__float32", dev)
+    assert cm.schedule.plan.mode == "eager"
+    out = cm(d["inputs"][0].to(dev))
+    assert_close(out, d["outputs"][0], "float32", "no-fusion output")
+
+
+def test_profile_kernels_reports_every_kernel(dev):
+    d, cm = _model("block__default__float32", dev, cuda_graphs=False)
+    rows = cm.profile_kernels([t.to(dev) for t in d["inputs"]], iters=3)
+    assert [r[0] for r in rows] == [k.name for k in cm.schedule.kernels]
+    assert all(r[2] > 0 for r in rows)
+
+
+def test_source_is_exposed_per_kernel(dev):
+    d, cm = _model("block__default__float32", dev)
+    assert 'extern "C" __global__' in cm.source()
+    name = cm.schedule.generated()[0].name
+    assert "__launch_bounds__" in cm.kernel_source(name)
+    assert cm.source_path().exists()
+    info = cm._module.kernel_info(name)
+    assert 0 < info["registers"] <= 255
+
+
+def test_backend_selection_has_no_silent_fallback(dev):
+    from mlc_compiler_b200.executor import CompiledModel, select_backend
+    from mlc_compiler_b200.runtime import BackendError
+
+    d = load_tiny("pointwise__default__float32")
+    with pytest.raises(ValueError, match="Triton"):
+        select_backend(Config(backend="triton"), dev)
+    with pytest.raises(BackendError):
+        CompiledModel(d["schedule"], d["params"], Config(), "cpu")
+
+
+def test_dependent_launch_variant_gives_the_same_answer(dev):
+    d, cm = _model("block__default__float32", dev, dependent_launch=True)
+    x = d["inputs"][0].to(dev)
+    cm(x)
+    out = cm(x)
+    assert_close(out, d["outputs"][0], "float32", "dependent-launch output")
