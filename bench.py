@@ -174,7 +174,8 @@ def time_end_to_end(cm, host_inputs, steps: int, warmup: int, flush) -> tuple[li
     return times, h2d, d2h
 
 
-def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64) -> list[dict]:
+def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64,
+                   only: str | None = None, **cfg_kw) -> list[dict]:
     """Each fused-kernel microbenchmark as a CUDA graph of ``launches`` launches
     cycling over buffer sets whose total size exceeds 4x L2, so every launch
     reads and writes HBM."""
@@ -186,13 +187,15 @@ def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64)
     rows = []
     for name in ("micro-layernorm", "micro-softmax", "micro-gelu"):
         for b in batches:
+            if only and only != f"{name}:{b}":
+                continue
             sched = load_schedule(models.schedule_name(name, b, torch.float16))
             k = sched.generated()[0]
-            rt = CudaRuntime(sched, Config(), dev)
+            rt = CudaRuntime(sched, Config(**cfg_kw), dev)
             spec = rt.generated.launch[k.name]
             model, inputs = models.build(name, b, dtype=torch.float16)
-            table = dict(model.named_parameters())
-            table.update(dict(model.named_buffers()))
+            table = dict(model.named_parameters(remove_duplicate=False))
+            table.update(dict(model.named_buffers(remove_duplicate=False)))
             big = [n for n in set(k.reads()) | set(k.writes()) if n not in sched.params]
             per_set = sum(sched.buffers[n].nbytes for n in big)
             sets = max(2, min(4096, -(-4 * l2 // per_set)))
@@ -242,29 +245,43 @@ def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64)
     return rows
 
 
-def in_model_families(cm, dev_inputs, peak_gbs: float) -> list[dict]:
-    """Device time of the generated kernels inside the BERT step, by function."""
-    rows = cm.profile_kernels(dev_inputs, iters=20)
+def in_model_families(cm, dev_inputs, peak_gbs: float, reps: int = 20) -> list[dict]:
+    """Device time of each distinct generated function inside the BERT step: one
+    bound launch of it replayed ``reps`` times inside a CUDA graph (in place, so
+    it runs out of L2 and is launch-bound at batch 1; reported for context)."""
+    cm(*dev_inputs)
+    torch.cuda.synchronize()
     table = cm.launch_table
-    agg: dict[str, dict] = {}
-    extern_ms = 0.0
-    for name, summary, ms in rows:
-        if name not in table:
-            extern_ms += ms
-            continue
-        sym = table[name]["symbol"]
-        a = agg.setdefault(sym, {"symbol": sym, "example": summary.split(": ", 1)[1][:60],
-                                 "launches": 0, "ms": 0.0, "alg_bytes": table[name]["alg_bytes"]})
-        a["launches"] += 1
-        a["ms"] += ms
+    groups: dict[str, list[str]] = {}
+    for name, row in table.items():
+        groups.setdefault(row["symbol"], []).append(name)
     out = []
-    for a in sorted(agg.values(), key=lambda r: -r["ms"]):
-        us = a["ms"] * 1e3 / a["launches"]
-        out.append({"symbol": a["symbol"], "example": a["example"], "launches": a["launches"],
-                    "us_per_launch": round(us, 3), "alg_bytes": a["alg_bytes"],
-                    "gbs": round(a["alg_bytes"] / us / 1e3, 1),
-                    "frac": round(a["alg_bytes"] / us / 1e3 / peak_gbs, 4)})
-    out.append({"symbol": "extern (cuBLAS/ATen)", "ms_total": round(extern_ms, 4)})
+    for sym, names in groups.items():
+        kind, fn = cm._bound[names[0]]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(5):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1e3 / (5 * reps)
+        ab = table[names[0]]["alg_bytes"]
+        out.append({"symbol": sym, "kernel": cm.schedule.kernel(names[0]).summary().split(": ", 1)[1][:70],
+                    "launches_per_forward": len(names), "us_per_launch": round(us, 3),
+                    "alg_bytes": ab, "gbs": round(ab / us / 1e3, 1),
+                    "frac": round(ab / us / 1e3 / peak_gbs, 4), "l2_resident": True})
+    out.sort(key=lambda r: -r["us_per_launch"] * r["launches_per_forward"])
     return out
 
 
@@ -276,8 +293,8 @@ def cpu_oracle_times(steps: int, warmup: int) -> tuple[list[float], int, str]:
 
     sched = load_schedule("bert-base_b1_s128_float16")
     model, inputs = models.build("bert-base", 1, dtype=torch.float16)
-    table = dict(model.named_parameters())
-    table.update(dict(model.named_buffers()))
+    table = dict(model.named_parameters(remove_duplicate=False))
+    table.update(dict(model.named_buffers(remove_duplicate=False)))
     buffers = oracle.allocate(sched, table, inputs)
     times = []
     for i in range(warmup + steps):
@@ -351,7 +368,13 @@ def run_ours(args) -> int:
     peak, peak_kind = _peaks()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
-    cm, host_inputs, sched = _compiled("bert-base", 1, torch.float16, dev)
+    cfg_kw = dict(kv.split("=") for kv in args.cfg)
+    cfg_kw = {k: (v == "True" if v in ("True", "False") else int(v)) for k, v in cfg_kw.items()}
+    if args.section == "micro":
+        rows = micro_roofline(dev, peak, only=args.only, **cfg_kw)
+        print(json.dumps({"fused_kernels": rows, "cfg": cfg_kw}))
+        return 0
+    cm, host_inputs, sched = _compiled("bert-base", 1, torch.float16, dev, **cfg_kw)
     dev_inputs = [t.to(dev) for t in host_inputs]
     flush = L2Flush(dev)
     cm(*dev_inputs)
@@ -366,12 +389,17 @@ def run_ours(args) -> int:
     ms = reduce_scalar(statistics.mean(per_step), "max", world, dev)
     med = reduce_scalar(statistics.median(per_step), "max", world, dev)
 
+    if args.section == "model":
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": round(ms, 5), "unit": "ms",
+                              "steps": steps, "warmup": warmup, "cfg": cfg_kw}))
+        return 0
     e2e_times, h2d, d2h = time_end_to_end(cm, host_inputs, steps, warmup, flush)
     e2e_ms = reduce_scalar(statistics.mean(e2e_times), "max", world, dev)
 
     # batch 32 split over the ranks, independent replicas
     per_gpu = 32 // world
-    tcm, tin, tsched = _compiled("bert-base", per_gpu, torch.float16, dev)
+    tcm, tin, tsched = _compiled("bert-base", per_gpu, torch.float16, dev, **cfg_kw)
     tdev = [t.to(dev) for t in tin]
     tms = statistics.mean(time_replays(tcm, tdev, max(5, steps // 4), 3, flush))
     seqs = reduce_scalar(per_gpu / (tms / 1e3), "sum", world, dev)
@@ -398,7 +426,7 @@ def run_ours(args) -> int:
     }
 
     if rank == 0:
-        micro = micro_roofline(dev, peak, batches=(1, 8, 32))
+        micro = micro_roofline(dev, peak, batches=(1, 8, 32), **cfg_kw)
         top = max(micro, key=lambda r: r["alg_bytes"])
         line["roofline"] = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
                             "frac": top["frac"], "traffic": None,
@@ -427,6 +455,13 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--section", default="all", choices=("all", "micro", "model"),
+                    help="'micro' prints only the fused-kernel microbenchmark table, "
+                         "'model' only the device-timed BERT step (both for profiling)")
+    ap.add_argument("--only", default=None, metavar="KERNEL:BATCH",
+                    help="with --section micro: one row, e.g. micro-gelu:8")
+    ap.add_argument("--cfg", action="append", default=[], metavar="KEY=VALUE",
+                    help="override a Config field (e.g. dependent_launch=True)")
     args = ap.parse_args()
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 

@@ -45,9 +45,12 @@ class Config:
     reduction_packs_per_thread: int = 4
     #: force the number of threads that share one row (0 = choose)
     reduction_group: int = 0
+    #: kernels whose every output is fp16/bf16 may use SFU-based exp/tanh/erf and
+    #: division (error ~1e-6, below half-precision resolution); fp32 kernels never do
+    narrow_fast_math: bool = True
     #: launch generated kernels with programmatic stream serialisation and emit
     #: the matching grid-dependency instructions
-    dependent_launch: bool = False
+    dependent_launch: bool = True
 
     @property
     def effective_launch_bytes(self) -> float:

@@ -8,10 +8,12 @@
 //
 // Arithmetic conventions (they are what parity with the torch reference backend
 // rests on): fp16/bf16 operands are widened to fp32 on load and all float math
-// is fp32 with IEEE division and square root, no fused multiply-add contraction
-// (the module is compiled with --fmad=false) and no fast-math; a value whose IR
-// dtype is fp16/bf16 is held in a float register that always contains an exactly
-// representable narrow value.
+// is fp32 with IEEE division and square root and no fused multiply-add
+// contraction (the module is compiled with --fmad=false, never with fast-math);
+// a value whose IR dtype is fp16/bf16 is held in a float register that always
+// contains an exactly representable narrow value.  Kernels that store only
+// fp16/bf16 may use the SFU-based forms further down (error ~1e-6 relative,
+// invisible after the narrow rounding); kernels with an fp32 output never do.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -114,13 +116,49 @@ __device__ __forceinline__ void mlcb_load_at(const T* __restrict__ p,
     for (int i = 0; i < W; ++i) dst[at + i] = tmp[i];
 }
 
+// Register array -> packed storage words.  fp16/bf16 convert two registers per
+// instruction (cvt.rn.f16x2.f32 / cvt.rn.bf16x2.f32).
+template <typename T, int W>
+struct mlcb_packer {
+    static __device__ __forceinline__ void run(mlcb_pack<T, W>& u,
+                                               const typename mlcb_elem<T>::reg (&src)[W]) {
+#pragma unroll
+        for (int i = 0; i < W; ++i) u.e[i] = mlcb_elem<T>::put(src[i]);
+    }
+};
+template <int W>
+struct mlcb_packer<__half, W> {
+    static __device__ __forceinline__ void run(mlcb_pack<__half, W>& u, const float (&src)[W]) {
+        if constexpr (W % 2 == 0) {
+            __half2* h = reinterpret_cast<__half2*>(u.e);
+#pragma unroll
+            for (int i = 0; i < W / 2; ++i) h[i] = __floats2half2_rn(src[2 * i], src[2 * i + 1]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < W; ++i) u.e[i] = __float2half_rn(src[i]);
+        }
+    }
+};
+template <int W>
+struct mlcb_packer<__nv_bfloat16, W> {
+    static __device__ __forceinline__ void run(mlcb_pack<__nv_bfloat16, W>& u, const float (&src)[W]) {
+        if constexpr (W % 2 == 0) {
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(u.e);
+#pragma unroll
+            for (int i = 0; i < W / 2; ++i) h[i] = __floats2bfloat162_rn(src[2 * i], src[2 * i + 1]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < W; ++i) u.e[i] = __float2bfloat16_rn(src[i]);
+        }
+    }
+};
+
 template <typename T, int W>
 __device__ __forceinline__ void mlcb_store(T* __restrict__ p,
                                            const typename mlcb_elem<T>::reg (&src)[W]) {
     mlcb_pack<T, W> u;
     typedef typename mlcb_pack<T, W>::word word;
-#pragma unroll
-    for (int i = 0; i < W; ++i) u.e[i] = mlcb_elem<T>::put(src[i]);
+    mlcb_packer<T, W>::run(u, src);
     word* q = reinterpret_cast<word*>(p);
 #pragma unroll
     for (int i = 0; i < mlcb_pack<T, W>::N; ++i) q[i] = u.w[i];
@@ -154,6 +192,27 @@ __device__ __forceinline__ float  mlcb_sigmoid(float x)  { return 1.0f / (1.0f +
 __device__ __forceinline__ double mlcb_sigmoid(double x) { return 1.0 / (1.0 + exp(-x)); }
 __device__ __forceinline__ float  mlcb_rsqrt(float x)  { return 1.0f / sqrtf(x); }
 __device__ __forceinline__ double mlcb_rsqrt(double x) { return 1.0 / sqrt(x); }
+// SFU-based forms used only where the result is rounded to fp16/bf16 before it
+// is stored (absolute error about 2e-7, far below half-precision resolution).
+__device__ __forceinline__ float mlcb_rcp(float x) { return __frcp_rn(x); }
+__device__ __forceinline__ float mlcb_tanh_fast(float x) {
+    // 1 - 2 / (1 + e^(2x)): exact limits at +-inf, NaN propagates
+    return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x));
+}
+__device__ __forceinline__ float mlcb_sigmoid_fast(float x) {
+    return __fdividef(1.0f, 1.0f + __expf(-x));
+}
+__device__ __forceinline__ float mlcb_erf_fast(float x) {
+    // Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7
+    const float ax = fabsf(x);
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    float p = fmaf(1.061405429f, t, -1.453152027f);
+    p = fmaf(p, t, 1.421413741f);
+    p = fmaf(p, t, -0.284496736f);
+    p = fmaf(p, t, 0.254829592f);
+    const float r = 1.0f - p * t * __expf(-ax * ax);
+    return copysignf(r, x);
+}
 __device__ __forceinline__ i64 mlcb_ipow(i64 b, i64 e) {
     if (e < 0) return (b == 1) ? 1 : ((b == -1) ? ((e & 1) ? -1 : 1) : 0);
     i64 r = 1;

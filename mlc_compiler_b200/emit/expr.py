@@ -49,8 +49,41 @@ _TORCH_FN = {
 }
 
 _COMPARE = {"gt": ">", "lt": "<", "ge": ">=", "le": "<=", "eq": "==", "ne": "!="}
+_FAST_UNARY = {"exp": "__expf", "log": "__logf", "tanh": "mlcb_tanh_fast",
+               "erf": "mlcb_erf_fast", "sigmoid": "mlcb_sigmoid_fast", "rsqrt": "rsqrtf"}
 _FLOAT_UNARY = {"exp": "exp", "log": "log", "sqrt": "sqrt", "sin": "sin", "cos": "cos",
                 "tanh": "tanh", "erf": "erf"}
+
+
+#: When set, float32 transcendentals and divisions use the SFU-based forms
+#: (``__expf``, ``__fdividef`` and the closed forms in the device header), whose
+#: error (~1e-6 relative, ~2e-7 absolute for erf/tanh) is four orders below the
+#: half-precision rounding of the value that is finally stored.  The emitters
+#: switch it on only for kernels all of whose outputs are fp16/bf16; kernels
+#: with an fp32/fp64 output keep IEEE division and the full-precision libm.
+_FAST = False
+
+
+class math_mode:
+    """``with math_mode(fast): ...`` around the rendering of one kernel."""
+
+    def __init__(self, fast: bool):
+        self.fast = bool(fast)
+
+    def __enter__(self):
+        global _FAST
+        self.prev, _FAST = _FAST, self.fast
+        return self
+
+    def __exit__(self, *exc):
+        global _FAST
+        _FAST = self.prev
+
+
+def wants_fast_math(k, cfg) -> bool:
+    outs = list(k.outputs)
+    return (bool(getattr(cfg, "narrow_fast_math", True)) and bool(outs)
+            and all(a.dtype in kir.NARROW_FLOATS for a in outs))
 
 
 @dataclass(frozen=True)
@@ -225,7 +258,19 @@ def render_call(fn: str, args: list[Val]) -> Val:
         ct = rdt
         xs = [convert(x.code, x.dtype, ct) for x in args]
         m = _opmath(ct)
-        if fn in _FLOAT_UNARY:
+        fast = _FAST and m == "float"
+        if fast and fn in _FAST_UNARY:
+            code = f"{_FAST_UNARY[fn]}({xs[0]})"
+        elif fast and fn == "div":
+            if args[0].varies and not args[1].varies:
+                # divisor is a row statistic: one reciprocal per row, hoisted by the
+                # compiler out of the unrolled element loop
+                code = f"({xs[0]} * mlcb_rcp({xs[1]}))"
+            else:
+                code = f"__fdividef({xs[0]}, {xs[1]})"
+        elif fast and fn == "reciprocal":
+            code = f"__fdividef(1.0f, {xs[0]})"
+        elif fn in _FLOAT_UNARY:
             code = f"{_fname(_FLOAT_UNARY[fn], ct)}({xs[0]})"
         elif fn == "neg":
             code = f"(-{xs[0]})"
@@ -297,10 +342,65 @@ def render(e: Expr, loads: list[Val], refs: dict[str, Val]) -> Val:
         x = render(e.x, loads, refs)
         return Val(convert(x.code, x.dtype, e.dtype), e.dtype, x.dim, x.varies)
     if isinstance(e, Call):
+        if e.fn == "div" and isinstance(e.args[1], Const) and _is_pow2(e.args[1].value):
+            # x / 2^k == x * 2^-k in IEEE arithmetic, and a multiply is one
+            # instruction where a correctly rounded divide is about ten
+            c = e.args[1]
+            recip = Const(1.0 / float(c.value), c.dtype if c.dtype in kir.FLOAT_DTYPES else None)
+            num = render(e.args[0], loads, refs)
+            if is_float(num.dtype):
+                return render_call("mul", [num, const_val(recip)])
         return render_call(e.fn, [render(a, loads, refs) for a in e.args])
     raise TypeError(f"cannot emit {type(e).__name__}")
+
+
+def _is_pow2(v) -> bool:
+    if isinstance(v, bool) or not isinstance(v, (int, float)):
+        return False
+    f = float(v)
+    if f == 0.0 or f != f or math.isinf(f):
+        return False
+    m, _ = math.frexp(abs(f))
+    return m == 0.5 and 2.0 ** -100 < abs(f) < 2.0 ** 100
 
 
 def promoted_load_dtype(dtype: str) -> str:
     """fp16/bf16 operands are computed on as fp32 (``torch_backend.py:53-62``)."""
     return "float32" if dtype in kir.NARROW_FLOATS else dtype
+
+
+def store_only_casts(binds, out_expr: dict, outputs) -> set[str]:
+    """Names of ``t = Cast(y, narrow)`` temps whose only readers are stores to
+    buffers of that same narrow dtype.  The store converts fp32 -> fp16/bf16 with
+    the same round-to-nearest-even, so rounding in the body as well would only
+    repeat it; such a temp is carried in fp32 and rounded once, at the store."""
+    uses: dict[str, int] = {}
+    for _, e in binds:
+        for sub in kir.walk(e):
+            if isinstance(sub, Ref):
+                uses[sub.name] = uses.get(sub.name, 0) + 1
+    out_dtype = {a.name: a.dtype for a in outputs}
+    store_uses: dict[str, list[str]] = {}
+    for oname, e in out_expr.items():
+        if isinstance(e, Ref):
+            store_uses.setdefault(e.name, []).append(out_dtype.get(oname))
+        else:
+            for sub in kir.walk(e):
+                if isinstance(sub, Ref):
+                    uses[sub.name] = uses.get(sub.name, 0) + 1
+    found = set()
+    for name, e in binds:
+        if (isinstance(e, Cast) and e.dtype in kir.NARROW_FLOATS and uses.get(name, 0) == 0
+                and store_uses.get(name) and all(d == e.dtype for d in store_uses[name])):
+            found.add(name)
+    return found
+
+
+def render_bind(name: str, e: Expr, loads, refs, elide: set[str]) -> Val:
+    """Render one temp; a store-only narrowing cast of an fp32 value is carried
+    unrounded (see :func:`store_only_casts`)."""
+    if name in elide and isinstance(e, Cast):
+        x = render(e.x, loads, refs)
+        if x.dtype == "float32":
+            return Val(x.code, e.dtype, x.dim, x.varies)
+    return render(e, loads, refs)

@@ -63,6 +63,11 @@ def _chunks(acc: Access, v: int):
 
 def emit_pointwise(k: kir.PointwiseKernel, cfg, buffers: dict[str, kir.BufferSpec] | None = None,
                    name: str | None = None) -> tuple[str, LaunchSpec]:
+    with X.math_mode(X.wants_fast_math(k, cfg)):
+        return _emit_pointwise(k, cfg, buffers, name)
+
+
+def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
     name = name or k.name
     numel = k.numel
     operands = list(k.inputs) + list(k.outputs)
@@ -149,8 +154,9 @@ def emit_pointwise(k: kir.PointwiseKernel, cfg, buffers: dict[str, kir.BufferSpe
         L.append(f"        const {it} idx = i0 + j;")
     L += inner
     refs: dict[str, X.Val] = {}
+    elide = X.store_only_casts(k.body, k.out_expr, k.outputs)
     for temp, e in k.body:
-        v = X.render(e, loads, refs)
+        v = X.render_bind(temp, e, loads, refs, elide)
         L.append(f"        const {X.REG_T[v.dtype]} {temp} = {v.code};")
         refs[temp] = X.Val(temp, v.dtype, v.dim)
     for i, a in enumerate(k.outputs):

@@ -144,6 +144,16 @@ class _Ctx:
 
     def __init__(self, k: kir.ReductionKernel, geo: Geometry, it: str):
         self.k, self.geo, self.it = k, geo, it
+        self.elide = X.store_only_casts([(s.name, s.expr) for s in k.steps if isinstance(s, Bind)],
+                                        {n: e for n, e in k.out_expr.items()
+                                         if n not in k.row_outputs},
+                                        [a for a in k.outputs if a.name not in k.row_outputs])
+        # a temp also read by a Reduce or a row output must keep its rounding
+        for s in k.steps:
+            if isinstance(s, Reduce):
+                self.elide -= kir.expr_refs(s.expr)
+        for n in k.row_outputs:
+            self.elide -= kir.expr_refs(k.out_expr[n])
         self.lines: list[str] = []
         self.vec = varying_steps(k)
         self.scalars: dict[str, X.Val] = {}   # rendered row scalars (binds + reduces)
@@ -356,7 +366,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
             probe.update(pre_vals)
             tmp_refs = dict(probe)
             for s in vbinds:
-                v = X.render(s.expr, loads, tmp_refs)
+                v = X.render_bind(s.name, s.expr, loads, tmp_refs, c.elide)
                 tmp_refs[s.name] = X.Val(s.name, v.dtype, v.dim, True)
             rv = X.render(red.expr, loads, tmp_refs)
             rdt = X.reduce_type(red.kind, rv.dtype)
@@ -366,7 +376,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
         tmp_refs = dict(c.scalars)
         tmp_refs.update(pre_vals)
         for s in vbinds:
-            v = X.render(s.expr, loads, tmp_refs)
+            v = X.render_bind(s.name, s.expr, loads, tmp_refs, c.elide)
             tmp_refs[s.name] = X.Val(s.name, v.dtype, v.dim, True)
             if s.name in kept:
                 c.emit(f"    {X.REG_T[v.dtype]} a_{s.name}[{NP}][{V}];")
@@ -408,7 +418,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
             local = dict(c.scalars)
             local.update(pre_vals)
             for s in vbinds:
-                v = X.render(s.expr, loads, local)
+                v = X.render_bind(s.name, s.expr, loads, local, c.elide)
                 c.emit(f"{in2}const {X.REG_T[v.dtype]} {s.name} = {v.code};")
                 local[s.name] = X.Val(s.name, v.dtype, v.dim, True)
                 if s.name in kept:
@@ -629,7 +639,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
         # result types first (needed to declare accumulators)
         probe = dict(c.scalars)
         for b in p.binds:
-            v = X.render(b.expr, loads, probe)
+            v = X.render_bind(b.name, b.expr, loads, probe, c.elide)
             probe[b.name] = X.Val(b.name, v.dtype, v.dim, True)
         accs = {}
         if online is not None:
@@ -680,7 +690,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
                    f"(in{i} + in{i}_r + ({_col_off(a, 'col')}));  // {a.name}")
         local = dict(c.scalars)
         for b in p.binds:
-            v = X.render(b.expr, loads, local)
+            v = X.render_bind(b.name, b.expr, loads, local, c.elide)
             c.emit(f"{in2}const {X.REG_T[v.dtype]} {b.name} = {v.code};")
             local[b.name] = X.Val(b.name, v.dtype, v.dim, True)
         if online is not None:
@@ -705,6 +715,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
             # m' = max(m, max(pack)); l' = l * exp(m - m') + sum(exp(x - m')).
             # A lane that has only met -inf keeps l = 0 and never evaluates
             # exp(-inf - -inf).
+            ex = "__expf" if X._FAST else "expf"
             c.emit(f"{ind}float pm = xs[0];")
             c.emit("#pragma unroll")
             c.emit(f"{ind}for (int j = 1; j < {V}; ++j) pm = mlcb_max<float>(pm, xs[j]);")
@@ -712,13 +723,13 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
             c.emit(f"{ind}if (nm != MLCB_NINF_F) {{")
             c.emit(f"{ind}    float ps = 0.0f;")
             c.emit("#pragma unroll")
-            c.emit(f"{ind}    for (int j = 0; j < {V}; ++j) ps += expf(xs[j] - nm);")
-            c.emit(f"{ind}    run_l = run_l * ((run_m == MLCB_NINF_F) ? 0.0f : expf(run_m - nm)) + ps;")
+            c.emit(f"{ind}    for (int j = 0; j < {V}; ++j) ps += {ex}(xs[j] - nm);")
+            c.emit(f"{ind}    run_l = run_l * ((run_m == MLCB_NINF_F) ? 0.0f : {ex}(run_m - nm)) + ps;")
             c.emit(f"{ind}    run_m = nm;")
             c.emit(f"{ind}}}")
         for i, a in stores:
             ac, st = acc_out[i], X.STORAGE_T[a.dtype]
-            if ac.width == V:
+            if ac.width == V and V > 1:
                 c.emit(f"{ind}if (live) mlcb_store<{st}, {V}>(out{i} + out{i}_r + "
                        f"({_col_off(a, 'c0')}), o{i});")
             elif ac.width > 1:
@@ -736,7 +747,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
             else:
                 c.emit(f"    const float {mx.name} = mlcb_group_reduce<mlcb_op_max, {G}, float>(run_m);")
             c.emit(f"    const float scaled_l = (run_m == MLCB_NINF_F) ? 0.0f : "
-                   f"run_l * expf(run_m - {mx.name});")
+                   f"run_l * {'__expf' if X._FAST else 'expf'}(run_m - {mx.name});")
             if geo.cta_row:
                 c.emit(f"    const float {sm.name} = mlcb_cta_reduce<mlcb_op_sum, {nw}, float>(scaled_l, "
                        f"reinterpret_cast<float*>(mlcb_red + 1 * 32));")
@@ -777,4 +788,5 @@ def emit_reduction(k: kir.ReductionKernel, cfg, buffers: dict[str, kir.BufferSpe
         for a in list(k.inputs) + list(k.outputs):
             check_bounds(a.index, buffers[a.buffer].numel, f"{k.name}:{a.name}")
     name = name or k.name
-    return _emit_streamed(k, cfg, name) if k.two_pass else _emit_persistent(k, cfg, name)
+    with X.math_mode(X.wants_fast_math(k, cfg)):
+        return _emit_streamed(k, cfg, name) if k.two_pass else _emit_persistent(k, cfg, name)

@@ -376,7 +376,9 @@ class CompiledModel:
 
 def _tensor_table(params) -> dict[str, torch.Tensor]:
     if isinstance(params, torch.nn.Module):
-        table = dict(params.named_parameters())
-        table.update(dict(params.named_buffers()))
+        # tied weights appear once in named_parameters(); a schedule may name
+        # either key, so keep duplicates (and non-persistent buffers)
+        table = dict(params.named_parameters(remove_duplicate=False))
+        table.update(dict(params.named_buffers(remove_duplicate=False)))
         return table
     return dict(params)
