@@ -307,30 +307,8 @@ def cpu_oracle_times(steps: int, warmup: int) -> tuple[list[float], int, str]:
 
 # --------------------------------------------------------------------------
 
-def dist_setup(n: int):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    return rank, world, local
-
-
-def reduce_scalar(x: float, op: str, world: int, dev) -> float:
-    if world == 1:
-        return x
-    import torch.distributed as dist
-    t = torch.tensor([x], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
-    return float(t.item())
-
-
-def barrier(world: int):
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
+def barrier(group) -> None:
+    group.barrier()
     torch.cuda.synchronize()
 
 
@@ -362,9 +340,13 @@ def run_reference(args) -> int:
 def run_ours(args) -> int:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the generated kernels have no CPU path")
-    rank, world, local = dist_setup(args.gpus)
+    from mlc_compiler_b200.replicas import ReplicaGroup, replicated_throughput
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    group = ReplicaGroup.from_env(backend="nccl", device=dev)
+    rank, world = group.rank, group.world
     peak, peak_kind = _peaks()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
@@ -380,14 +362,14 @@ def run_ours(args) -> int:
     cm(*dev_inputs)
     torch.cuda.synchronize()
 
-    barrier(world)
+    barrier(group)
     with ClockSampler(local) as clocks:
         t_wall = time.perf_counter()
         per_step = time_replays(cm, dev_inputs, steps, warmup, flush)
-        barrier(world)
+        barrier(group)
         wall = time.perf_counter() - t_wall
-    ms = reduce_scalar(statistics.mean(per_step), "max", world, dev)
-    med = reduce_scalar(statistics.median(per_step), "max", world, dev)
+    ms = group.max(statistics.mean(per_step), dev)
+    med = group.max(statistics.median(per_step), dev)
 
     if args.section == "model":
         if rank == 0:
@@ -395,15 +377,14 @@ def run_ours(args) -> int:
                               "steps": steps, "warmup": warmup, "cfg": cfg_kw}))
         return 0
     e2e_times, h2d, d2h = time_end_to_end(cm, host_inputs, steps, warmup, flush)
-    e2e_ms = reduce_scalar(statistics.mean(e2e_times), "max", world, dev)
+    e2e_ms = group.max(statistics.mean(e2e_times), dev)
 
     # batch 32 split over the ranks, independent replicas
     per_gpu = 32 // world
     tcm, tin, tsched = _compiled("bert-base", per_gpu, torch.float16, dev, **cfg_kw)
     tdev = [t.to(dev) for t in tin]
     tms = statistics.mean(time_replays(tcm, tdev, max(5, steps // 4), 3, flush))
-    seqs = reduce_scalar(per_gpu / (tms / 1e3), "sum", world, dev)
-    slow = reduce_scalar(tms, "max", world, dev)
+    thr = replicated_throughput(group, per_gpu, tms, dev)
 
     line = {
         "metric": METRIC, "value": round(ms, 5), "unit": "ms", "n_gpus": world, "steps": steps,
@@ -419,9 +400,9 @@ def run_ours(args) -> int:
         "gpu_launches": cm.generated_launches * steps,
         "clocks": clocks.summary(),
         "timed_region_wall_s": round(wall, 3),
-        "replica_throughput": {"model": "bert-base fp16 s128", "global_batch": per_gpu * world,
-                               "per_gpu_batch": per_gpu, "seq_per_s": round(seqs, 1),
-                               "ms_per_forward": round(slow, 4),
+        "replica_throughput": {"model": "bert-base fp16 s128", "global_batch": thr["global_batch"],
+                               "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
+                               "ms_per_forward": round(thr["ms_per_forward"], 4),
                                "arena_mb_per_gpu": round(tsched.arena_bytes / 2**20, 2)},
     }
 
@@ -439,12 +420,10 @@ def run_ours(args) -> int:
             times, cores, sample = cpu_oracle_times(10, 1)
             line["cpu_baseline"] = {"value": round(statistics.mean(times), 3), "unit": "ms",
                                     "cores": cores, "kind": "port", "sample": f"10 {sample}"}
-    barrier(world)
+    barrier(group)
     if rank == 0:
         print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    group.close()
     return 0
 
 
