@@ -352,6 +352,54 @@ def run_ours(args) -> int:
 
     cfg_kw = dict(kv.split("=") for kv in args.cfg)
     cfg_kw = {k: (v == "True" if v in ("True", "False") else int(v)) for k, v in cfg_kw.items()}
+    if args.section == "families":
+        fcm, fin, fs = _compiled(args.model, args.batch, getattr(torch, args.dtype), dev, **cfg_kw)
+        fdev = [t.to(dev) for t in fin]
+        fam = in_model_families(fcm, fdev, peak)
+        lat = statistics.median(time_replays(fcm, fdev, 50, 10, lambda: None))
+        print(json.dumps({"model": args.model, "batch": args.batch, "dtype": args.dtype,
+                          "median_ms_no_flush": round(lat, 5), "kernels": len(fs),
+                          "generated_us": round(sum(r["us_per_launch"] * r["launches_per_forward"]
+                                                    for r in fam), 1), "families": fam}))
+        return 0
+    if args.section == "compare":
+        # same method as the reference's own harness (mlc/bench/runner.py:84-112):
+        # median of 50 event-timed calls of compiled(*inputs) after 20 warm-ups, no flush
+        rows = []
+        for name, tag in (("bert-base", ""), ("gpt2-small", ""), ("gpt2-small", "ref")):
+            for dt in ("float16", "bfloat16"):
+                for b in (1, 8, 32):
+                    if tag and dt != "float16":
+                        continue
+                    from mlc_compiler_b200 import Config, models
+                    from mlc_compiler_b200.executor import CompiledModel
+                    from mlc_compiler_b200.frontend import load_schedule, schedule_path
+                    stem = models.schedule_name(name, b, getattr(torch, dt), tag=tag)
+                    if not schedule_path(stem).exists():
+                        continue
+                    sch = load_schedule(stem)
+                    model, inputs = models.build(name, b, dtype=getattr(torch, dt),
+                                                 **sch.meta.get("variant", {}))
+                    cmx = CompiledModel(sch, model, Config(**cfg_kw), dev)
+                    di = [t.to(dev) for t in inputs]
+                    for _ in range(20):
+                        cmx(*di)
+                    torch.cuda.synchronize()
+                    ts = []
+                    for _ in range(50):
+                        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        s0.record()
+                        cmx(*di)
+                        e0.record()
+                        e0.synchronize()
+                        ts.append(s0.elapsed_time(e0))
+                    rows.append({"model": stem, "kernels": len(sch), "median_ms": round(statistics.median(ts), 4),
+                                 "p10_ms": round(sorted(ts)[5], 4),
+                                 "arena_mb": round(sch.arena_bytes / 2**20, 2),
+                                 "peak_alloc_mb": round(torch.cuda.max_memory_allocated(dev) / 2**20, 1)})
+                    del cmx
+        print(json.dumps({"compare": rows, "cfg": cfg_kw}))
+        return 0
     if args.section == "micro":
         rows = micro_roofline(dev, peak, only=args.only, **cfg_kw)
         print(json.dumps({"fused_kernels": rows, "cfg": cfg_kw}))
@@ -394,6 +442,7 @@ def run_ours(args) -> int:
         "config": {"workload": WORKLOAD, "kernels": len(sched), "generated": cm.generated_launches,
                    "arena_kib": round(sched.arena_bytes / 1024, 1),
                    "l2": "flushed between steps (256 MiB write)",
+                   "graph_streams": cm.cfg.graph_streams, "dependent_launch": cm.cfg.dependent_launch,
                    "parallelism": f"{world} independent replicas, no collectives"},
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
@@ -434,9 +483,12 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--section", default="all", choices=("all", "micro", "model"),
+    ap.add_argument("--section", default="all", choices=("all", "micro", "model", "families", "compare"),
                     help="'micro' prints only the fused-kernel microbenchmark table, "
                          "'model' only the device-timed BERT step (both for profiling)")
+    ap.add_argument("--model", default="bert-base")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--dtype", default="float16")
     ap.add_argument("--only", default=None, metavar="KERNEL:BATCH",
                     help="with --section micro: one row, e.g. micro-gelu:8")
     ap.add_argument("--cfg", action="append", default=[], metavar="KEY=VALUE",

@@ -50,7 +50,11 @@ class Config:
     narrow_fast_math: bool = True
     #: launch generated kernels with programmatic stream serialisation and emit
     #: the matching grid-dependency instructions
-    dependent_launch: bool = True
+    dependent_launch: bool = False
+    #: streams the schedule is captured over.  1 reproduces the reference's single
+    #: chain of graph nodes; more lets kernels with no dependency between them
+    #: (physical byte ranges considered) run as parallel branches of the graph
+    graph_streams: int = 4
 
     @property
     def effective_launch_bytes(self) -> float:

@@ -24,7 +24,7 @@ from typing import Any, Mapping, Sequence
 
 import torch
 
-from . import kir
+from . import concurrency, kir
 from .config import Config
 from .runtime import BackendError, CudaRuntime, LaunchRun
 
@@ -148,6 +148,20 @@ class CompiledModel:
                                 .contiguous().reshape(-1))
 
         self._module = CudaRuntime(schedule, self.cfg, self.device)
+        # Execution order and arena actually used.  With more than one capture
+        # stream the kernels are re-ordered by data level and the arena re-packed
+        # so that independent neighbours (q/k/v projections, embedding gathers)
+        # become parallel branches of the CUDA graph; the kernels themselves and
+        # ``self.schedule`` are untouched.
+        self._exec = schedule
+        self._streams = None
+        n_streams = int(getattr(self.cfg, "graph_streams", 1) or 1)
+        if n_streams > 1 and self.cfg.cuda_graphs and schedule.plan.mode == "arena":
+            relaxed = concurrency.relax(schedule)
+            plan = concurrency.assign_streams(concurrency.dependencies(relaxed), n_streams)
+            if plan.forked:
+                self._exec, self._streams = relaxed, plan
+                self._side = [torch.cuda.Stream(device=self.device) for _ in range(n_streams - 1)]
         self._arena: torch.Tensor | None = None
         self._resident: dict[str, torch.Tensor] | None = None
         self._plan: list | None = None
@@ -171,7 +185,7 @@ class CompiledModel:
         return torch.empty(spec.numel, dtype=kir.torch_dtype(spec.dtype), device=self.device)
 
     def _get_arena(self) -> torch.Tensor:
-        need = max(self.schedule.arena_bytes, 1)
+        need = max(self._exec.arena_bytes, 1)
         if self._arena is None or self._arena.numel() < need:
             self._arena = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self._arena
@@ -179,7 +193,7 @@ class CompiledModel:
     def _resident_buffers(self, inputs: Sequence[torch.Tensor]) -> dict[str, torch.Tensor]:
         self._check_inputs(inputs)
         if self._resident is None:
-            sch = self.schedule
+            sch = self._exec
             buffers = dict(self.params)
             for b in sch.buffers.values():
                 if b.name in buffers or b.plannable or b.name not in self._live:
@@ -208,21 +222,27 @@ class CompiledModel:
         plan: list = []
         run: list = []
         self._bound: dict[str, Any] = {}
+        self._per_kernel: list = []
 
         def flush():
             if run:
                 plan.append(("cuda", LaunchRun(self._module.lib, list(run))))
                 run.clear()
 
-        for k in self.schedule.kernels:
+        for k in self._exec.kernels:
             if isinstance(k, kir.ExternKernel):
                 flush()
                 b = bind_extern(k, buffers)
                 self._bound[k.name] = ("extern", b)
+                self._per_kernel.append(("extern", b))
                 plan.append(("extern", b))
             elif isinstance(k, (kir.PointwiseKernel, kir.ReductionKernel)):
-                fn = self._module.bind(k, buffers)[0]
+                flags = None
+                if getattr(self.cfg, "dependent_launch", False) == "chain" and not run:
+                    flags = 0      # first of a run: its predecessor is a library kernel
+                fn = self._module.bind(k, buffers, flags)[0]
                 self._bound[k.name] = ("cuda", fn)
+                self._per_kernel.append(("cuda", fn))
                 run.append(fn)
             else:
                 raise ExecutionError(f"cannot execute {type(k).__name__}")
@@ -232,11 +252,44 @@ class CompiledModel:
     def run_kernels(self, buffers: dict[str, torch.Tensor] | None = None) -> None:
         if self._plan is None:
             raise ExecutionError("no launch plan: call the model (or forward) once first")
+        if self._streams is not None:
+            return self._run_forked()
         for kind, payload in self._plan:
             if kind == "cuda":
                 payload()
             else:
                 run_bound_extern(payload)
+
+    def _run_forked(self) -> None:
+        """Enqueue the plan over several streams: a kernel goes to the stream the
+        plan gave it and waits (by event) for predecessors enqueued elsewhere.
+        Under capture the events become edges of the graph; outside capture the
+        same code is the warm-up.  Everything rejoins the calling stream."""
+        sp = self._streams
+        main = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(main)
+        used: set[int] = set()
+        done: dict[int, torch.cuda.Event] = {}
+        for j, (kind, payload) in enumerate(self._per_kernel):
+            t = sp.stream[j]
+            stream = main if t == 0 else self._side[t - 1]
+            if t != 0 and t not in used:
+                stream.wait_event(start)
+                used.add(t)
+            for p in sp.waits[j]:
+                stream.wait_event(done[p])
+            with torch.cuda.stream(stream):
+                if kind == "cuda":
+                    payload[payload.grid]()
+                else:
+                    run_bound_extern(payload)
+            if j in sp.signals:
+                ev = torch.cuda.Event()
+                ev.record(stream)
+                done[j] = ev
+        for t in sorted(used):
+            main.wait_stream(self._side[t - 1])
 
     def run_one(self, k, buffers: dict[str, torch.Tensor]) -> None:
         if isinstance(k, kir.ExternKernel):

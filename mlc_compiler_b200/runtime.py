@@ -295,13 +295,14 @@ class CudaRuntime:
             names.append(a.buffer if isinstance(a, kir.Operand) else a.value.buffer.name)
         return names
 
-    def bind(self, k, buffers: dict[str, torch.Tensor]):
+    def bind(self, k, buffers: dict[str, torch.Tensor], flags: int | None = None):
         if self._is_extern(k):
             raise TypeError("extern kernels do not go through the CUDA runtime")
         spec = self.generated.launch[k.name]
         tensors = tuple(buffers[n] for n in self._buffer_names(k))
         fn = BoundLaunch(self.lib, self.loaded.kernel(self.generated.symbol[k.name]), k.name,
-                         spec.grid, spec.block, spec.smem, self.flags, tensors)
+                         spec.grid, spec.block, spec.smem,
+                         self.flags if flags is None else flags, tensors)
         return fn, spec.grid, tensors, {}
 
     def launch(self, k, buffers: dict[str, torch.Tensor]) -> None:

@@ -129,3 +129,23 @@ def test_dependent_launch_variant_gives_the_same_answer(dev):
     cm(x)
     out = cm(x)
     assert_close(out, d["outputs"][0], "float32", "dependent-launch output")
+
+
+def test_forked_graph_is_bitwise_equal_to_the_serial_chain(dev):
+    """Capturing over several streams changes only the edges of the graph."""
+    from mlc_compiler_b200 import models
+    from mlc_compiler_b200.executor import CompiledModel
+    from mlc_compiler_b200.frontend import load_schedule
+
+    s = load_schedule("bert-base_b1_s128_float16")
+    model, inputs = models.build("bert-base", 1, dtype=torch.float16)
+    di = [t.to(dev) for t in inputs]
+    serial = CompiledModel(s, model, Config(graph_streams=1), dev)
+    forked = CompiledModel(s, model, Config(graph_streams=4), dev)
+    assert forked._streams is not None and forked._streams.forked >= 40
+    a = serial(*di).clone()
+    forked(*di)
+    for _ in range(3):
+        b = forked(*di).clone()
+        assert torch.equal(a, b)
+    assert [k.name for k in forked.schedule.kernels] == [k.name for k in s.kernels]
