@@ -51,6 +51,9 @@ class Config:
     #: launch generated kernels with programmatic stream serialisation and emit
     #: the matching grid-dependency instructions
     dependent_launch: bool = False
+    #: fold a pointwise producer into the pointwise kernels that only re-read it at
+    #: another index (bias add + head-layout copy at batch > 1); bit-identical
+    forward_into_copies: bool = True
     #: streams the schedule is captured over.  1 reproduces the reference's single
     #: chain of graph nodes; more lets kernels with no dependency between them
     #: (physical byte ranges considered) run as parallel branches of the graph

@@ -189,7 +189,22 @@ def store_code(v: X.Val, out_dtype: str) -> str:
     rounds a float register to fp16/bf16, so a float32 (or already narrow)
     value is passed through rather than rounded twice."""
     if out_dtype in kir.NARROW_FLOATS and v.dtype in ("float32", out_dtype):
-        return v.code
+        return _strip_round(v.code, out_dtype)
     if out_dtype in kir.NARROW_FLOATS:
         return X.convert(v.code, v.dtype, "float32")
     return X.convert(v.code, v.dtype, out_dtype)
+
+
+def _strip_round(code: str, dtype: str) -> str:
+    """``mlcb_rn_f16(x)`` handed to an fp16 store is ``x``: the store rounds the
+    same way (likewise bf16).  Only a call wrapping the whole expression counts."""
+    head = "mlcb_rn_f16(" if dtype == "float16" else "mlcb_rn_bf16("
+    if not (code.startswith(head) and code.endswith(")")):
+        return code
+    depth = 0
+    for i, ch in enumerate(code[len(head) - 1:]):
+        depth += ch == "("
+        depth -= ch == ")"
+        if depth == 0:
+            return code[len(head):-1] if i == len(code) - len(head) else code
+    return code

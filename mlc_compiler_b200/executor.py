@@ -24,7 +24,7 @@ from typing import Any, Mapping, Sequence
 
 import torch
 
-from . import concurrency, kir
+from . import concurrency, kir, rewrite
 from .config import Config
 from .runtime import BackendError, CudaRuntime, LaunchRun
 
@@ -129,7 +129,26 @@ class CompiledModel:
             self.device = torch.device("cuda", torch.cuda.current_device())
         self.backend = select_backend(self.cfg, self.device)
 
-        self._live = schedule.live_buffers()
+        # What actually runs.  ``self.schedule`` stays what the frontend produced;
+        # ``self._exec`` may (1) have pointwise producers folded into the copies
+        # that read them and (2) be re-ordered by data level with a re-packed
+        # arena, so that independent neighbours (q/k/v projections, embedding
+        # gathers) become parallel branches of the CUDA graph.  Generated and
+        # library kernels are otherwise exactly the scheduled ones.
+        work = schedule
+        if getattr(self.cfg, "forward_into_copies", True) and schedule.plan.mode == "arena":
+            work = rewrite.forward_into_consumers(schedule)
+        self._exec = work
+        self._streams = None
+        n_streams = int(getattr(self.cfg, "graph_streams", 1) or 1)
+        if n_streams > 1 and self.cfg.cuda_graphs and work.plan.mode == "arena":
+            relaxed = concurrency.relax(work)
+            plan = concurrency.assign_streams(concurrency.dependencies(relaxed), n_streams)
+            if plan.forked:
+                self._exec, self._streams = relaxed, plan
+                self._side = [torch.cuda.Stream(device=self.device) for _ in range(n_streams - 1)]
+
+        self._live = self._exec.live_buffers()
         self.params: dict[str, torch.Tensor] = {}
         source = _tensor_table(params)
         for buf, origin in schedule.params.items():
@@ -147,21 +166,7 @@ class CompiledModel:
             self.params[buf] = (t.detach().to(self.device, kir.torch_dtype(spec.dtype))
                                 .contiguous().reshape(-1))
 
-        self._module = CudaRuntime(schedule, self.cfg, self.device)
-        # Execution order and arena actually used.  With more than one capture
-        # stream the kernels are re-ordered by data level and the arena re-packed
-        # so that independent neighbours (q/k/v projections, embedding gathers)
-        # become parallel branches of the CUDA graph; the kernels themselves and
-        # ``self.schedule`` are untouched.
-        self._exec = schedule
-        self._streams = None
-        n_streams = int(getattr(self.cfg, "graph_streams", 1) or 1)
-        if n_streams > 1 and self.cfg.cuda_graphs and schedule.plan.mode == "arena":
-            relaxed = concurrency.relax(schedule)
-            plan = concurrency.assign_streams(concurrency.dependencies(relaxed), n_streams)
-            if plan.forked:
-                self._exec, self._streams = relaxed, plan
-                self._side = [torch.cuda.Stream(device=self.device) for _ in range(n_streams - 1)]
+        self._module = CudaRuntime(self._exec, self.cfg, self.device)
         self._arena: torch.Tensor | None = None
         self._resident: dict[str, torch.Tensor] | None = None
         self._plan: list | None = None
@@ -169,7 +174,7 @@ class CompiledModel:
         self._graph_replay = None
         self._static_outputs: Any = None
         #: generated-kernel launches per forward (what a bench reports)
-        self.generated_launches = len(schedule.generated())
+        self.generated_launches = len(self._exec.generated())
 
     # -- allocation ------------------------------------------------------------
     def _check_inputs(self, inputs: Sequence[torch.Tensor]) -> None:
@@ -303,7 +308,7 @@ class CompiledModel:
         """The unplanned baseline: allocate each intermediate when it is first
         written, drop it after its last read (``executor.py:216-228``)."""
         self._check_inputs(inputs)
-        sch, plan = self.schedule, self.schedule.plan
+        sch, plan = self._exec, self._exec.plan
         buffers = dict(self.params)
         for v, t in zip(sch.inputs, inputs):
             spec = sch.buffers[v.buffer]
@@ -322,7 +327,7 @@ class CompiledModel:
         return buffers
 
     def forward(self, *inputs: torch.Tensor):
-        if self.schedule.plan.mode == "eager":
+        if self._exec.plan.mode == "eager":
             return self._collect(self._run_eager(inputs))
         buffers = self._resident_buffers(inputs)
         if self._plan is None:
@@ -395,7 +400,7 @@ class CompiledModel:
         start = torch.cuda.Event(enable_timing=True)
         end = torch.cuda.Event(enable_timing=True)
         out = []
-        for k in self.schedule.kernels:
+        for k in self._exec.kernels:
             entry = self._bound[k.name]
             for _ in range(3):
                 run(entry)
@@ -409,6 +414,11 @@ class CompiledModel:
         return out
 
     # -- introspection -------------------------------------------------------------
+    @property
+    def executed_schedule(self) -> kir.Schedule:
+        """The schedule as launched: after producer forwarding and re-ordering."""
+        return self._exec
+
     def source(self) -> str:
         return self._module.source
 

@@ -1,0 +1,259 @@
+"""Schedule rewrites applied by the executor before code generation.
+
+``forward_into_consumers`` removes a class of kernels the reference's fusion
+pass cannot: a pointwise producer whose only readers are pointwise kernels that
+read it *at a different index* -- typically ``mm + bias`` over ``[B*T, D]``
+followed, at batch > 1, by the ``clone`` that lays the heads out as
+``[B, H, T, D/H]`` (or transposed for K).  The reference refuses to fuse them
+because one iteration would need a value another iteration computed
+(``reads_are_local``, ``mlc/lower.py:117-155``), and so launches the bias kernel,
+writes ``[B*T, D]``, and reads it straight back in the copy.  Every element of
+the producer is independent, however, so the consumer can simply *recompute*
+the producer's expression at the index it wants: compose the consumer's read
+map with each producer operand's map, inline the body, drop the producer.  The
+copy then reads the matmul output directly and the intermediate buffer is never
+written (36 launches and 36 round trips through memory fewer per BERT-base
+forward at batch > 1).  Results are bit-identical: the inlined value is rounded
+to the intermediate's dtype exactly where the store used to round it.
+
+Composition is done on the ``(size, out_stride, in_stride)`` terms.  The
+consumer's map turns its index into digits ``d_k`` with weights ``s_k``
+(``x = base + sum d_k s_k``); a producer operand's term ``((x / o) % n) * s``
+selects the digits whose weight lies in ``[o, o n)``.  When every digit falls
+wholly inside, below or above that window (and the base cannot carry across
+it) the composite is again a list of terms; otherwise the rewrite is skipped
+for that producer.
+"""
+
+from __future__ import annotations
+
+from . import kir
+from .kir import Call, Cast, Const, Load, Ref
+
+
+class _NoCompose(Exception):
+    pass
+
+
+def compose(outer: kir.IndexMap, inner: kir.IndexMap, inner_numel: int) -> kir.IndexMap:
+    """Map ``idx_c -> inner(outer(idx_c))`` where ``outer`` yields a position in
+    the producer's flat iteration space and ``inner`` is one of its operands."""
+    if len(outer.axes) != 1 or len(inner.axes) > 1:
+        raise _NoCompose
+    ax = outer.axes[0]
+    digits = sorted(ax.terms, key=lambda t: t[2])
+    reach = 0
+    for n, _, s in digits:                       # non-overlapping mixed radix
+        if s <= 0 or s < reach:
+            raise _NoCompose
+        reach = s * n
+    new_terms: list[tuple[int, int, int]] = []
+    base = inner.base
+    terms = inner.axes[0].terms if inner.axes else ()
+    for n, o, s in terms:
+        top = o * n
+        modulo = top != inner_numel              # the outermost term carries no '%'
+        low_max = outer.base % o
+        mid = outer.base // o
+        mid = mid % n if modulo else mid
+        inside_max = mid
+        for nk, ok, sk in digits:
+            if sk * nk <= o:
+                low_max += (nk - 1) * sk
+            elif sk % o == 0 and (not modulo or sk * nk <= top):
+                new_terms.append((nk, ok, (sk // o) * s))
+                inside_max += (nk - 1) * (sk // o)
+            elif modulo and sk % top == 0:
+                continue
+            else:
+                raise _NoCompose
+        if low_max >= o or (modulo and inside_max >= n):
+            raise _NoCompose
+        base += mid * s
+    new_terms = [t for t in new_terms if t[2] != 0]
+    new_terms.sort(key=lambda t: -t[1])
+    return kir.IndexMap((kir.Axis(ax.var, ax.numel, tuple(new_terms)),), base)
+
+
+def _rename(e, prefix: str, slot_map: dict[int, int]):
+    if isinstance(e, Load):
+        return Load(slot_map[e.slot])
+    if isinstance(e, Ref):
+        return Ref(prefix + e.name)
+    if isinstance(e, Call):
+        return Call(e.fn, tuple(_rename(a, prefix, slot_map) for a in e.args))
+    if isinstance(e, Cast):
+        return Cast(_rename(e.x, prefix, slot_map), e.dtype)
+    return e
+
+
+def _substitute(e, mapping: dict[int, object]):
+    if isinstance(e, Load):
+        return mapping.get(e.slot, e)
+    if isinstance(e, Call):
+        return Call(e.fn, tuple(_substitute(a, mapping) for a in e.args))
+    if isinstance(e, Cast):
+        return Cast(_substitute(e.x, mapping), e.dtype)
+    return e
+
+
+def _identity_output(k: kir.PointwiseKernel) -> bool:
+    if len(k.outputs) != 1:
+        return False
+    m = k.outputs[0].index
+    return (m.base == 0 and len(m.axes) == 1
+            and m.axes[0].terms in (((k.numel, 1, 1),), ()) and (k.numel > 1 or not m.axes[0].terms))
+
+
+def _inline(producer: kir.PointwiseKernel, consumer: kir.PointwiseKernel, tag: str):
+    """``consumer`` with every read of the producer's buffer replaced by the
+    producer's expression; raises ``_NoCompose`` when a map does not compose."""
+    x = producer.outputs[0]
+    inputs = list(consumer.inputs)
+    body: list[tuple[str, object]] = []
+    replace: dict[int, object] = {}
+    drop: list[int] = []
+    n = 0
+    for j, arg in enumerate(consumer.inputs):
+        if arg.buffer != x.buffer:
+            continue
+        prefix = f"{tag}{n}_"
+        n += 1
+        slot_map: dict[int, int] = {}
+        for i, a in enumerate(producer.inputs):
+            m = compose(arg.index, a.index, producer.numel)
+            for q, have in enumerate(inputs):
+                if have.buffer == a.buffer and have.dtype == a.dtype and have.index == m and q not in drop:
+                    slot_map[i] = q
+                    break
+            else:
+                inputs.append(kir.Operand(a.name, a.buffer, a.dtype, m))
+                slot_map[i] = len(inputs) - 1
+        for name, e in producer.body:
+            body.append((prefix + name, _rename(e, prefix, slot_map)))
+        value = _rename(producer.out_expr[x.name], prefix, slot_map)
+        # what the consumer used to load: the value rounded to the buffer's dtype,
+        # widened again if that dtype is a narrow float
+        value = Cast(value, x.dtype)
+        if x.dtype in kir.NARROW_FLOATS:
+            value = Cast(value, "float32")
+        replace[j] = value
+        drop.append(j)
+    if not drop:
+        return consumer
+    # renumber the remaining loads
+    keep = [q for q in range(len(inputs)) if q not in drop]
+    renum = {old: new for new, old in enumerate(keep)}
+
+    def fix(e):
+        if isinstance(e, Load):
+            if e.slot in replace:
+                return fix(replace[e.slot])
+            return Load(renum[e.slot])
+        if isinstance(e, Call):
+            return Call(e.fn, tuple(fix(a) for a in e.args))
+        if isinstance(e, Cast):
+            return Cast(fix(e.x), e.dtype)
+        return e
+
+    new_body = [(nm, fix(e)) for nm, e in body] + [(nm, fix(e)) for nm, e in consumer.body]
+    out_expr = {nm: fix(e) for nm, e in consumer.out_expr.items()}
+    return kir.PointwiseKernel(consumer.name, consumer.space, [inputs[q] for q in keep],
+                               list(consumer.outputs), new_body, out_expr,
+                               list(producer.ops) + list(consumer.ops))
+
+
+def forward_into_consumers(schedule: kir.Schedule, max_body: int = 32,
+                           max_consumers: int = 4, replan: bool = True) -> kir.Schedule:
+    """Inline eligible pointwise producers into their pointwise consumers and
+    drop them.  Returns a new schedule (kernels keep their names; the dropped
+    producer's buffer stays in the table, unused).
+
+    A consumer now reads the producer's operands, which the original arena plan
+    considered dead by then.  With ``replan`` the arena is re-packed afterwards
+    from the new live ranges (``concurrency.relax``); without it a producer is
+    only forwarded when no kernel up to its last consumer reuses its operands'
+    bytes."""
+    kernels = list(schedule.kernels)
+    outputs = {v.buffer for v in schedule.outputs}
+    changed = True
+    tag = 0
+    while changed:
+        changed = False
+        for pi, p in enumerate(kernels):
+            if not isinstance(p, kir.PointwiseKernel) or not _identity_output(p):
+                continue
+            x = p.outputs[0]
+            if x.buffer in outputs or not schedule.buffers[x.buffer].plannable:
+                continue
+            if len(p.body) > max_body or x.buffer in p.reads():
+                continue
+            readers = [ci for ci, c in enumerate(kernels) if ci != pi and x.buffer in c.reads()]
+            writers = [ci for ci, c in enumerate(kernels) if ci != pi and x.buffer in c.writes()]
+            if not readers or writers or len(readers) > max_consumers or min(readers) < pi:
+                continue
+            if not all(isinstance(kernels[ci], kir.PointwiseKernel) for ci in readers):
+                continue
+            # never make a consumer move more bytes than the load it replaces
+            heavy = sum(min(a.index.distinct_elements(), p.numel) * kir.ITEMSIZE[a.dtype]
+                        for a in p.inputs)
+            if heavy > schedule.buffers[x.buffer].nbytes + 65536:
+                continue
+            # a producer operand must still hold the same data when the consumer runs
+            stable = True
+            for a in p.inputs:
+                for ci in range(pi + 1, max(readers) + 1):
+                    if a.buffer in kernels[ci].writes():
+                        stable = False
+            if not stable or (not replan and _arena_clobbered(schedule, kernels, p, pi, max(readers))):
+                continue
+            try:
+                new = {ci: _inline(p, kernels[ci], f"f{tag}") for ci in readers}
+            except _NoCompose:
+                continue
+            tag += 1
+            for ci, c in new.items():
+                kernels[ci] = c
+            del kernels[pi]
+            changed = True
+            break
+    if len(kernels) == len(schedule.kernels):
+        return schedule
+    out = kir.Schedule(name=schedule.name, kernels=kernels, buffers=schedule.buffers,
+                       inputs=schedule.inputs, outputs=schedule.outputs, params=schedule.params,
+                       plan=schedule.plan, meta=dict(schedule.meta))
+    if replan:
+        from .concurrency import relax
+
+        live = out.live_buffers()
+        out.plan = kir.ArenaPlan(out.plan.mode, out.plan.arena_bytes,
+                                 {b: o for b, o in out.plan.offsets.items() if b in live},
+                                 out.plan.peak_bytes, out.plan.total_bytes,
+                                 out.plan.alloc_at, out.plan.free_at)
+        out = relax(out)
+    return out
+
+
+def _arena_clobbered(schedule, kernels, p, pi: int, last_reader: int) -> bool:
+    """True when the arena bytes of one of the producer's operands are reused by a
+    kernel that runs before the last consumer: reading the operand later would
+    then see someone else's data."""
+    if schedule.plan.mode != "arena":
+        return False
+    off = schedule.plan.offsets
+
+    def span(b):
+        if b in off and schedule.buffers[b].plannable:
+            return off[b], off[b] + schedule.buffers[b].nbytes
+        return None
+
+    for a in p.inputs:
+        sa = span(a.buffer)
+        if sa is None:
+            continue
+        for ci in range(pi + 1, last_reader + 1):
+            for b in kernels[ci].writes():
+                sb = span(b)
+                if sb is not None and b != a.buffer and sa[0] < sb[1] and sb[0] < sa[1]:
+                    return True
+    return False

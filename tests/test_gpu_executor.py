@@ -66,7 +66,9 @@ def test_kernels_never_write_outside_their_arena_slices(dev):
         shifted.plan.offsets[n] = s.plan.offsets[n] * 2 + pad
         live_end[n] = shifted.plan.offsets[n] + s.buffers[n].nbytes
     shifted.plan.arena_bytes = s.plan.arena_bytes * 2 + 2 * pad + 4096
-    cm = CompiledModel(shifted, d["params"], Config(cuda_graphs=False), dev)
+    cm = CompiledModel(shifted, d["params"],
+                       Config(cuda_graphs=False, forward_into_copies=False, graph_streams=1), dev)
+    assert cm.executed_schedule.plan.offsets == shifted.plan.offsets
     arena = cm._get_arena()
     arena.fill_(0xA5)
     out = cm(d["inputs"][0].to(dev))
@@ -98,7 +100,7 @@ def test_unplanned_schedule_runs_the_eager_path(dev):
 def test_profile_kernels_reports_every_kernel(dev):
     d, cm = _model("block__default__float32", dev, cuda_graphs=False)
     rows = cm.profile_kernels([t.to(dev) for t in d["inputs"]], iters=3)
-    assert [r[0] for r in rows] == [k.name for k in cm.schedule.kernels]
+    assert [r[0] for r in rows] == [k.name for k in cm.executed_schedule.kernels]
     assert all(r[2] > 0 for r in rows)
 
 
