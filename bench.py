@@ -277,7 +277,7 @@ def in_model_families(cm, dev_inputs, peak_gbs: float, reps: int = 20) -> list[d
         torch.cuda.synchronize()
         us = s.elapsed_time(e) * 1e3 / (5 * reps)
         ab = table[names[0]]["alg_bytes"]
-        out.append({"symbol": sym, "kernel": cm.schedule.kernel(names[0]).summary().split(": ", 1)[1][:70],
+        out.append({"symbol": sym, "kernel": cm.executed_schedule.kernel(names[0]).summary().split(": ", 1)[1][:70],
                     "launches_per_forward": len(names), "us_per_launch": round(us, 3),
                     "alg_bytes": ab, "gbs": round(ab / us / 1e3, 1),
                     "frac": round(ab / us / 1e3 / peak_gbs, 4), "l2_resident": True})
@@ -443,6 +443,7 @@ def run_ours(args) -> int:
                    "arena_kib": round(sched.arena_bytes / 1024, 1),
                    "l2": "flushed between steps (256 MiB write)",
                    "graph_streams": cm.cfg.graph_streams, "dependent_launch": cm.cfg.dependent_launch,
+                   "graph_branch_kernels": cm._streams.forked if cm._streams else 0,
                    "parallelism": f"{world} independent replicas, no collectives"},
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},

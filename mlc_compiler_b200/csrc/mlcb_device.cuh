@@ -194,23 +194,43 @@ __device__ __forceinline__ float  mlcb_rsqrt(float x)  { return 1.0f / sqrtf(x);
 __device__ __forceinline__ double mlcb_rsqrt(double x) { return 1.0 / sqrt(x); }
 // SFU-based forms used only where the result is rounded to fp16/bf16 before it
 // is stored (absolute error about 2e-7, far below half-precision resolution).
+// The .ftz variants are single MUFU instructions; the non-ftz intrinsics wrap
+// them in subnormal scaling that costs more than the operation itself.
+__device__ __forceinline__ float mlcb_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float mlcb_rcp_fast(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float mlcb_lg2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float mlcb_rcp(float x) { return __frcp_rn(x); }
+__device__ __forceinline__ float mlcb_exp_fast(float x) { return mlcb_ex2(x * 1.4426950408889634f); }
+__device__ __forceinline__ float mlcb_log_fast(float x) { return mlcb_lg2(x) * 0.6931471805599453f; }
+__device__ __forceinline__ float mlcb_div_fast(float a, float b) { return a * mlcb_rcp_fast(b); }
 __device__ __forceinline__ float mlcb_tanh_fast(float x) {
     // 1 - 2 / (1 + e^(2x)): exact limits at +-inf, NaN propagates
-    return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x));
+    return fmaf(-2.0f, mlcb_rcp_fast(1.0f + mlcb_ex2(x * 2.8853900817779268f)), 1.0f);
 }
 __device__ __forceinline__ float mlcb_sigmoid_fast(float x) {
-    return __fdividef(1.0f, 1.0f + __expf(-x));
+    return mlcb_rcp_fast(1.0f + mlcb_ex2(x * -1.4426950408889634f));
 }
 __device__ __forceinline__ float mlcb_erf_fast(float x) {
     // Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7
     const float ax = fabsf(x);
-    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    const float t = mlcb_rcp_fast(fmaf(0.3275911f, ax, 1.0f));
     float p = fmaf(1.061405429f, t, -1.453152027f);
     p = fmaf(p, t, 1.421413741f);
     p = fmaf(p, t, -0.284496736f);
     p = fmaf(p, t, 0.254829592f);
-    const float r = 1.0f - p * t * __expf(-ax * ax);
+    const float r = fmaf(-(p * t), mlcb_ex2(ax * ax * -1.4426950408889634f), 1.0f);
     return copysignf(r, x);
 }
 __device__ __forceinline__ i64 mlcb_ipow(i64 b, i64 e) {

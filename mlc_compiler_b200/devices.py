@@ -1,0 +1,171 @@
+"""Device profile for the cost model: the B200 entry the reference lacks.
+
+The reference prices fusion decisions from a per-device table
+(``mlc/devices.py:107-141``) that stops at Hopper; an unknown GPU silently gets
+A100 constants (``:141,161-165``).  This module supplies the Blackwell entry
+and a calibration that measures the three constants on the device itself
+through this backend's own runtime (the reference's probe is a Triton kernel,
+``mlc/bench/calibrate.py:46-59``):
+
+* streaming copy bandwidth (a generated 128-bit copy kernel over a buffer
+  larger than L2),
+* launch overhead, eager and inside a CUDA graph (an empty-ish kernel),
+* fp32 throughput (a dependent FMA chain per thread, many independent threads).
+
+From those it derives the reference's cost-model fields: ``flops_per_byte``,
+``launch_overhead_bytes`` and ``graph_launch_overhead_bytes``
+(``mlc/config.py:36-52``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from .config import Config
+
+
+@dataclass(frozen=True)
+class DeviceProfile:
+    name: str
+    #: sustained streaming copy bandwidth, bytes/s (read + write)
+    bandwidth: float
+    #: fp32 FMA throughput, FLOP/s
+    fp32_flops: float
+    #: seconds per eager launch / per captured graph node
+    launch_s: float
+    graph_launch_s: float
+    source: str = "table"
+
+    @property
+    def flops_per_byte(self) -> float:
+        return self.fp32_flops / self.bandwidth
+
+    @property
+    def launch_overhead_bytes(self) -> float:
+        return self.launch_s * self.bandwidth
+
+    @property
+    def graph_launch_overhead_bytes(self) -> float:
+        return self.graph_launch_s * self.bandwidth
+
+    def to_config(self, base: Config | None = None) -> Config:
+        """The reference's ``DeviceProfile.to_config`` (``mlc/devices.py:71-76``)."""
+        base = base or Config()
+        return base.replace(flops_per_byte=self.flops_per_byte,
+                            launch_overhead_bytes=self.launch_overhead_bytes,
+                            graph_launch_overhead_bytes=self.graph_launch_overhead_bytes)
+
+
+#: B200 (sm_100, 148 SMs, 1965 MHz boost): 148 x 128 lanes x 2 x 1.965 GHz = 74.5 TFLOP/s fp32;
+#: bandwidth is the measured large-copy figure on this pool, launch costs the
+#: measured per-node figures of a dependent kernel chain.
+B200 = DeviceProfile(name="NVIDIA B200", bandwidth=6.459e12, fp32_flops=74.5e12,
+                     launch_s=2.6e-6, graph_launch_s=1.0e-6)
+
+TABLE = {"b200": B200}
+
+
+def profile_for(device_name: str) -> DeviceProfile | None:
+    key = device_name.lower()
+    for tag, prof in TABLE.items():
+        if tag in key:
+            return prof
+    return None
+
+
+# --------------------------------------------------------------------------
+# calibration (needs a CUDA device)
+# --------------------------------------------------------------------------
+
+_PROBES = r"""
+extern "C" __global__ void __launch_bounds__(256) mlcb_probe_copy(const uint4* __restrict__ src,
+                                                                uint4* __restrict__ dst, long long n) {
+    long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long stride = (long long)gridDim.x * 256;
+    for (; i < n; i += stride) dst[i] = src[i];
+}
+extern "C" __global__ void mlcb_probe_empty(float* p) {
+    if (p == nullptr) p[0] = 0.0f;
+}
+extern "C" __global__ void __launch_bounds__(256) mlcb_probe_fma(float* out, int iters) {
+    float a = 1.0f + threadIdx.x * 1e-6f, b = 0.999f, c = 1e-3f;
+    float x0 = a, x1 = a + 1.0f, x2 = a + 2.0f, x3 = a + 3.0f;
+    for (int i = 0; i < iters; ++i) {
+        x0 = fmaf(x0, b, c); x1 = fmaf(x1, b, c); x2 = fmaf(x2, b, c); x3 = fmaf(x3, b, c);
+    }
+    if (x0 + x1 + x2 + x3 == -1.0f) out[0] = x0;
+}
+"""
+
+
+def calibrate(device="cuda", quick: bool = False) -> DeviceProfile:
+    """Measure the profile on ``device`` with CUDA events."""
+    import ctypes
+
+    import torch
+
+    from .runtime import LoadedModule, _check, compile_source
+
+    dev = torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    torch.cuda.set_device(index)
+    mod = LoadedModule(compile_source(_PROBES), index)
+    lib = mod.lib
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch(sym, grid, block, *vals):
+        arr = (ctypes.c_uint64 * len(vals))(*vals)
+        _check(lib, lib.mlcb_launch(mod.kernel(sym), grid, block, 0, arr, len(vals), stream, 0), sym)
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) * 1e-3 / reps
+
+    n_bytes = (256 if quick else 1024) << 20
+    src = torch.empty(n_bytes, dtype=torch.uint8, device=dev)
+    dst = torch.empty_like(src)
+    n_vec = n_bytes // 16
+    sm = torch.cuda.get_device_properties(index).multi_processor_count
+    t = timed(lambda: launch("mlcb_probe_copy", sm * 16, 256, src.data_ptr(), dst.data_ptr(), n_vec),
+              5 if quick else 20)
+    bandwidth = 2 * n_bytes / t
+
+    buf = torch.zeros(16, device=dev)
+    eager = timed(lambda: launch("mlcb_probe_empty", 1, 32, buf.data_ptr()), 2000)
+    g = torch.cuda.CUDAGraph()
+    nodes = 500
+    with torch.cuda.graph(g):
+        cs = torch.cuda.current_stream().cuda_stream
+        arr = (ctypes.c_uint64 * 1)(buf.data_ptr())
+        for _ in range(nodes):
+            _check(lib, lib.mlcb_launch(mod.kernel("mlcb_probe_empty"), 1, 32, 0, arr, 1, cs, 0), "probe")
+    graph = timed(g.replay, 20) / nodes
+
+    iters = 2048 if quick else 8192
+    # iters is a by-value int parameter; the shim passes 8-byte slots, the low 4 are read
+    tf = timed(lambda: launch("mlcb_probe_fma", sm * 8, 256, buf.data_ptr(), iters), 5)
+    flops = sm * 8 * 256 * 4 * 2 * iters / tf
+    return DeviceProfile(name=torch.cuda.get_device_name(index), bandwidth=bandwidth,
+                         fp32_flops=flops, launch_s=eager, graph_launch_s=graph, source="measured")
+
+
+def report(measured: DeviceProfile, table: DeviceProfile | None = None) -> str:
+    rows = [f"device            {measured.name} ({measured.source})",
+            f"copy bandwidth    {measured.bandwidth / 1e9:8.1f} GB/s",
+            f"fp32 throughput   {measured.fp32_flops / 1e12:8.2f} TFLOP/s",
+            f"launch            {measured.launch_s * 1e6:8.2f} us eager, "
+            f"{measured.graph_launch_s * 1e6:.2f} us per graph node",
+            f"flops_per_byte    {measured.flops_per_byte:8.2f}",
+            f"launch_overhead_bytes        {measured.launch_overhead_bytes:12.0f}",
+            f"graph_launch_overhead_bytes  {measured.graph_launch_overhead_bytes:12.0f}"]
+    if table is not None:
+        rows.append(f"table entry       {table.bandwidth / 1e9:.0f} GB/s, {table.fp32_flops / 1e12:.1f} TFLOP/s, "
+                    f"{table.launch_s * 1e6:.1f}/{table.graph_launch_s * 1e6:.1f} us")
+    return "\n".join(rows)

@@ -49,14 +49,14 @@ _TORCH_FN = {
 }
 
 _COMPARE = {"gt": ">", "lt": "<", "ge": ">=", "le": "<=", "eq": "==", "ne": "!="}
-_FAST_UNARY = {"exp": "__expf", "log": "__logf", "tanh": "mlcb_tanh_fast",
+_FAST_UNARY = {"exp": "mlcb_exp_fast", "log": "mlcb_log_fast", "tanh": "mlcb_tanh_fast",
                "erf": "mlcb_erf_fast", "sigmoid": "mlcb_sigmoid_fast", "rsqrt": "rsqrtf"}
 _FLOAT_UNARY = {"exp": "exp", "log": "log", "sqrt": "sqrt", "sin": "sin", "cos": "cos",
                 "tanh": "tanh", "erf": "erf"}
 
 
 #: When set, float32 transcendentals and divisions use the SFU-based forms
-#: (``__expf``, ``__fdividef`` and the closed forms in the device header), whose
+#: (``ex2/rcp.approx.ftz`` and the closed forms in the device header), whose
 #: error (~1e-6 relative, ~2e-7 absolute for erf/tanh) is four orders below the
 #: half-precision rounding of the value that is finally stored.  The emitters
 #: switch it on only for kernels all of whose outputs are fp16/bf16; kernels
@@ -267,9 +267,9 @@ def render_call(fn: str, args: list[Val]) -> Val:
                 # compiler out of the unrolled element loop
                 code = f"({xs[0]} * mlcb_rcp({xs[1]}))"
             else:
-                code = f"__fdividef({xs[0]}, {xs[1]})"
+                code = f"mlcb_div_fast({xs[0]}, {xs[1]})"
         elif fast and fn == "reciprocal":
-            code = f"__fdividef(1.0f, {xs[0]})"
+            code = f"mlcb_rcp_fast({xs[0]})"
         elif fn in _FLOAT_UNARY:
             code = f"{_fname(_FLOAT_UNARY[fn], ct)}({xs[0]})"
         elif fn == "neg":

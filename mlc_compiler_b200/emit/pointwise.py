@@ -76,8 +76,9 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
             check_bounds(a.index, buffers[a.buffer].numel, f"{k.name}:{a.name}")
 
     V = pick_vector(operands, numel)
-    # narrow V until nothing is forced into per-element access only because the
-    # pack is wider than the operand's contiguous run
+    tile = plan_tile(k, V)
+    if tile is not None:
+        return _emit_tiled(k, cfg, name, V, tile)
     packs = numel // V
     extents = [numel] + [a.index.bounds()[1] + 1 for a in operands]
     it = "i64" if needs_64bit(*extents) else "int"
@@ -208,3 +209,189 @@ def _strip_round(code: str, dtype: str) -> str:
         if depth == 0:
             return code[len(head):-1] if i == len(code) - len(head) else code
     return code
+
+
+# --------------------------------------------------------------------------
+# transposing kernels: V x V register tiles
+# --------------------------------------------------------------------------
+
+@dataclass
+class Tile:
+    """A second iteration digit ``r`` along which some operands are contiguous
+    while the outputs are contiguous along the innermost digit ``t``."""
+
+    n0: int        # size of the innermost digit t (out_stride 1)
+    nr: int        # size of digit r
+    o_r: int       # out_stride of digit r
+    along_r: dict  # input slot -> True if the operand also varies along t
+    along_t: dict  # input slot -> Access (contig / bcast, width V)
+
+
+def plan_tile(k: kir.PointwiseKernel, V: int) -> Tile | None:
+    """Decide whether ``k`` is a transposing kernel that can run on V x V
+    register tiles: every operand is 128-bit contiguous either along the
+    innermost iteration digit (all outputs are) or along one other digit."""
+    if V < 2 or not k.inputs or not k.outputs:
+        return None
+    numel = k.numel
+    along_t: dict[int, Access] = {}
+    gathers: list[int] = []
+    for i, a in enumerate(k.inputs):
+        acc = classify(a.index, "idx", V)
+        if acc.width == V:
+            along_t[i] = acc
+        else:
+            gathers.append(i)
+    if not gathers:
+        return None
+    for a in k.outputs:
+        acc = classify(a.index, "idx", V)
+        if acc.mode != "contig" or acc.width != V:
+            return None
+    digit = None
+    with_t: dict[int, bool] = {}
+    n0 = None
+    for i in gathers:
+        a = k.inputs[i]
+        ax = a.index.axis("idx")
+        if ax is None:
+            return None
+        unit = [t for t in ax.terms if t[2] == 1 and t[1] != 1]
+        if len(unit) != 1:
+            return None
+        nr, o_r, _ = unit[0]
+        if digit is None:
+            digit = (nr, o_r)
+        elif digit != (nr, o_r):
+            return None
+        if a.index.base % V:
+            return None
+        t_terms = [t for t in ax.terms if t[1] == 1]
+        if len(t_terms) > 1:
+            return None
+        for t in ax.terms:
+            if t is unit[0]:
+                continue
+            if t[2] % V:                      # keeps every run along r 16-byte aligned
+                return None
+            if t not in t_terms and t[1] % V:
+                return None
+        if t_terms:
+            if n0 is None:
+                n0 = t_terms[0][0]
+            elif n0 != t_terms[0][0]:
+                return None
+        with_t[i] = bool(t_terms)
+    nr, o_r = digit
+    if n0 is None:
+        n0 = o_r          # nothing fixes the t digit: take everything below r
+    if o_r % n0 or nr % (8 * V) or n0 % (4 * V) or numel % (o_r * nr):
+        return None
+    # operands contiguous along t must see runs that do not straddle the digit
+    for i, acc in along_t.items():
+        if acc.mode == "bcast" and acc.width != V:
+            return None
+    return Tile(n0=n0, nr=nr, o_r=o_r, along_r=with_t, along_t=along_t)
+
+
+def _emit_tiled(k: kir.PointwiseKernel, cfg, name: str, V: int, tile: Tile) -> tuple[str, LaunchSpec]:
+    """One thread owns a V x V tile: V consecutive values of digit r by V
+    consecutive values of the innermost digit t.  Operands contiguous along r are
+    fetched with V packed loads (one per t), operands and outputs contiguous
+    along t with one packed access per r; the transpose between the two happens
+    in registers, by indexing.  Lanes are laid out 4 along t by 8 along r so that
+    a warp-wide access covers whole 64- and 128-byte segments in both
+    directions: no shared memory, no barrier, no partially used sector."""
+    numel = k.numel
+    n0, nr, o_r = tile.n0, tile.nr, tile.o_r
+    operands = list(k.inputs) + list(k.outputs)
+    extents = [numel] + [a.index.bounds()[1] + 1 for a in operands]
+    it = "i64" if needs_64bit(*extents) else "int"
+    micro = numel // (V * V)
+    block = 128
+    while block > 32 and micro % block:
+        block //= 2
+    grid = (micro + block - 1) // block
+    WT, WR, M = n0 // (4 * V), nr // (8 * V), o_r // n0
+
+    aliased = {a.buffer for a in k.inputs} & {a.buffer for a in k.outputs}
+    params = []
+    for i, a in enumerate(k.inputs):
+        r = "" if a.buffer in aliased else " __restrict__"
+        params.append(f"const {X.STORAGE_T[a.dtype]}*{r} in{i}")
+    for i, a in enumerate(k.outputs):
+        r = "" if a.buffer in aliased else " __restrict__"
+        params.append(f"{X.STORAGE_T[a.dtype]}*{r} out{i}")
+
+    L: list[str] = []
+    L.append(f'extern "C" __global__ void __launch_bounds__({block}, {max(1, min(16, 512 // block))}) '
+             f'{name}({", ".join(params)}) {{')
+    L.append(f"    // transposing pointwise {list(k.space)} = {numel} elements; {V}x{V} register tile per "
+             f"thread over digits r=({nr} @ {o_r}) and t=({n0} @ 1); {grid} x {block} threads")
+    L.append("    MLCB_GRID_WAIT();")
+    L.append(f"    const {it} micro = ({it})blockIdx.x * {block} + threadIdx.x;")
+    if micro % block:
+        L.append(f"    if (micro >= {micro}) return;")
+    L.append(f"    const int lane = (int)(micro % 32);")
+    L.append(f"    const {it} w = micro / 32;")
+    L.append(f"    const {it} t_oct = (w % {WT}) * 4 + (lane % 4);")
+    L.append(f"    const {it} r_oct = ((w / {WT}) % {WR}) * 8 + (lane / 4);")
+    L.append(f"    const {it} rest = w / {WT * WR};")
+    L.append(f"    const {it} base_idx = t_oct * {V} + (rest % {M}) * {n0} + r_oct * {V * o_r} "
+             f"+ (rest / {M}) * {o_r * nr};")
+
+    loads: list[X.Val | None] = [None] * len(k.inputs)
+    for i, a in enumerate(k.inputs):
+        st, rt = X.STORAGE_T[a.dtype], X.REG_T[a.dtype]
+        vdt = X.promoted_load_dtype(a.dtype)
+        if i in tile.along_r:
+            if tile.along_r[i]:
+                L.append(f"    {rt} g{i}[{V}][{V}];  // {a.name}: contiguous along r")
+                L.append("#pragma unroll")
+                L.append(f"    for (int j = 0; j < {V}; ++j) mlcb_load<{st}, {V}>(in{i} + "
+                         f"({render_offset(a.index, {'idx': '(base_idx + j)'})}), g{i}[j]);")
+                loads[i] = X.Val(f"g{i}[j][i]", vdt)
+            else:
+                L.append(f"    {rt} g{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + "
+                         f"({render_offset(a.index, {'idx': 'base_idx'})}), g{i});  // {a.name}: along r only")
+                loads[i] = X.Val(f"g{i}[i]", vdt)
+    L.append("    MLCB_GRID_TRIGGER();")
+    L.append("#pragma unroll")
+    L.append(f"    for (int i = 0; i < {V}; ++i) {{")
+    L.append(f"        const {it} i0 = base_idx + i * {o_r};")
+    at_i0 = {"idx": "i0"}
+    for i, a in enumerate(k.inputs):
+        if i not in tile.along_t:
+            continue
+        acc = tile.along_t[i]
+        st, rt = X.STORAGE_T[a.dtype], X.REG_T[a.dtype]
+        vdt = X.promoted_load_dtype(a.dtype)
+        if acc.mode == "bcast":
+            L.append(f"        const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, at_i0)}));"
+                     f"  // {a.name}")
+            loads[i] = X.Val(f"v{i}", vdt)
+        else:
+            L.append(f"        {rt} v{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + ({render_offset(a.index, at_i0)}), v{i});"
+                     f"  // {a.name}")
+            loads[i] = X.Val(f"v{i}[j]", vdt)
+    for i, a in enumerate(k.outputs):
+        L.append(f"        {X.REG_T[a.dtype]} o{i}[{V}];")
+    L.append("#pragma unroll")
+    L.append(f"        for (int j = 0; j < {V}; ++j) {{")
+    refs: dict[str, X.Val] = {}
+    elide = X.store_only_casts(k.body, k.out_expr, k.outputs)
+    for temp, e in k.body:
+        v = X.render_bind(temp, e, loads, refs, elide)
+        L.append(f"            const {X.REG_T[v.dtype]} {temp} = {v.code};")
+        refs[temp] = X.Val(temp, v.dtype, v.dim)
+    for i, a in enumerate(k.outputs):
+        v = X.render(k.out_expr[a.name], loads, refs)
+        L.append(f"            o{i}[j] = {store_code(v, a.dtype)};  // {a.name}")
+    L.append("        }")
+    for i, a in enumerate(k.outputs):
+        L.append(f"        mlcb_store<{X.STORAGE_T[a.dtype]}, {V}>(out{i} + ({render_offset(a.index, at_i0)}), o{i});")
+    L.append("    }")
+    L.append("}")
+    spec = LaunchSpec(grid=grid, block=block, vector=V,
+                      alg_bytes=algorithmic_bytes(k.inputs, k.outputs, numel))
+    return "\n".join(L), spec

@@ -715,7 +715,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
             # m' = max(m, max(pack)); l' = l * exp(m - m') + sum(exp(x - m')).
             # A lane that has only met -inf keeps l = 0 and never evaluates
             # exp(-inf - -inf).
-            ex = "__expf" if X._FAST else "expf"
+            ex = "mlcb_exp_fast" if X._FAST else "expf"
             c.emit(f"{ind}float pm = xs[0];")
             c.emit("#pragma unroll")
             c.emit(f"{ind}for (int j = 1; j < {V}; ++j) pm = mlcb_max<float>(pm, xs[j]);")
@@ -747,7 +747,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
             else:
                 c.emit(f"    const float {mx.name} = mlcb_group_reduce<mlcb_op_max, {G}, float>(run_m);")
             c.emit(f"    const float scaled_l = (run_m == MLCB_NINF_F) ? 0.0f : "
-                   f"run_l * {'__expf' if X._FAST else 'expf'}(run_m - {mx.name});")
+                   f"run_l * {'mlcb_exp_fast' if X._FAST else 'expf'}(run_m - {mx.name});")
             if geo.cta_row:
                 c.emit(f"    const float {sm.name} = mlcb_cta_reduce<mlcb_op_sum, {nw}, float>(scaled_l, "
                        f"reinterpret_cast<float*>(mlcb_red + 1 * 32));")

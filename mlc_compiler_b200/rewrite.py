@@ -105,7 +105,15 @@ def _identity_output(k: kir.PointwiseKernel) -> bool:
             and m.axes[0].terms in (((k.numel, 1, 1),), ()) and (k.numel > 1 or not m.axes[0].terms))
 
 
-def _inline(producer: kir.PointwiseKernel, consumer: kir.PointwiseKernel, tag: str):
+def _next_prefix(consumer: kir.PointwiseKernel) -> int:
+    used = {nm.split("_", 1)[0] for nm, _ in consumer.body if nm.startswith("f") and "_" in nm}
+    n = 0
+    while f"f{n}" in used:
+        n += 1
+    return n
+
+
+def _inline(producer: kir.PointwiseKernel, consumer: kir.PointwiseKernel):
     """``consumer`` with every read of the producer's buffer replaced by the
     producer's expression; raises ``_NoCompose`` when a map does not compose."""
     x = producer.outputs[0]
@@ -113,11 +121,11 @@ def _inline(producer: kir.PointwiseKernel, consumer: kir.PointwiseKernel, tag: s
     body: list[tuple[str, object]] = []
     replace: dict[int, object] = {}
     drop: list[int] = []
-    n = 0
+    n = _next_prefix(consumer)
     for j, arg in enumerate(consumer.inputs):
         if arg.buffer != x.buffer:
             continue
-        prefix = f"{tag}{n}_"
+        prefix = f"f{n}_"
         n += 1
         slot_map: dict[int, int] = {}
         for i, a in enumerate(producer.inputs):
@@ -177,7 +185,6 @@ def forward_into_consumers(schedule: kir.Schedule, max_body: int = 32,
     kernels = list(schedule.kernels)
     outputs = {v.buffer for v in schedule.outputs}
     changed = True
-    tag = 0
     while changed:
         changed = False
         for pi, p in enumerate(kernels):
@@ -208,10 +215,9 @@ def forward_into_consumers(schedule: kir.Schedule, max_body: int = 32,
             if not stable or (not replan and _arena_clobbered(schedule, kernels, p, pi, max(readers))):
                 continue
             try:
-                new = {ci: _inline(p, kernels[ci], f"f{tag}") for ci in readers}
+                new = {ci: _inline(p, kernels[ci]) for ci in readers}
             except _NoCompose:
                 continue
-            tag += 1
             for ci, c in new.items():
                 kernels[ci] = c
             del kernels[pi]
