@@ -8,7 +8,9 @@ the fixtures it writes do not.  Two families:
 * ``tiny/<model>__<config>__<dtype>.pt`` -- the reference's ten small test
   modules (``tests/models.py:15-126`` there) under four pass configurations and
   three dtypes, plus LayerNorm / softmax modules at awkward row lengths
-  (1, 7, 33, 100, 1000, 1025 columns; 5 and 15 rows), persistent and streamed.
+  (1, 7, 33, 100, 1000, 1025 columns; 5 and 15 rows), persistent and streamed,
+  plus modules that touch every scalar function and every reduction kind in
+  fp32 / fp16 / bf16 / fp64 and int64.
   Each file holds the schedule (JSON), the parameters, the seeded
   inputs, the model outputs, and a snapshot of every buffer each kernel wrote,
   all computed by ``mlc.compile(..., Config(backend="torch"))`` on the CPU.
@@ -139,6 +141,68 @@ def make_odd(out_dir: pathlib.Path, reference: str) -> None:
                           flush=True)
 
 
+class EveryFloatFunction(torch.nn.Module):
+    """Touches every float scalar function of the kernel IR at least once."""
+
+    def forward(self, x, y):
+        a = torch.exp(x * 0.1) + torch.log(y) + torch.sqrt(y) + torch.rsqrt(y) + torch.reciprocal(y)
+        b = torch.sin(x) * torch.cos(x) + torch.tanh(x) + torch.erf(x) + torch.sigmoid(x) + torch.floor(x)
+        c = torch.maximum(x, y) - torch.minimum(x, y) + torch.pow(y, x * 0.1) + torch.abs(x) - (-x)
+        pick = torch.logical_or(x > y, torch.logical_and(x <= 0.0, torch.logical_not(x == y)))
+        d = torch.where(pick, a, b) + (x >= 0.5).to(x.dtype) + (x != y).to(x.dtype) + (x < 0).to(x.dtype)
+        e = torch.nn.functional.silu(x) + torch.relu(y) + torch.nn.functional.gelu(x, approximate="tanh")
+        return a / c.abs().clamp(min=0.5) + d, e + torch.nn.functional.gelu(y)
+
+
+class IntegerFunctions(torch.nn.Module):
+    def forward(self, i, j):
+        k = (i + j) * 3 - i.abs() + torch.maximum(i, j) - torch.minimum(i, j)
+        return k, torch.logical_and(i > j, j != 0), -i
+
+
+class ReductionKinds(torch.nn.Module):
+    """sum / max / min / prod, a count of booleans, mean and variance in one graph."""
+
+    def forward(self, x):
+        return (x.amin(-1), x.amax(-1), (x > 0).sum(-1), x.mean(-1), x.var(-1),
+                x.sum(-1, keepdim=True) * x)
+
+
+class ProductRows(torch.nn.Module):
+    def forward(self, s):
+        return (s * 0.25 + 1.0).prod(-1)
+
+
+def make_functions(out_dir: pathlib.Path) -> None:
+    """Coverage of the whole scalar function table and of every reduction kind,
+    in every float width, computed by the reference backend."""
+    from mlc_compiler_b200 import kir
+
+    out_dir.mkdir(parents=True, exist_ok=True)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(6, 40, generator=g) * 1.5
+    y = torch.rand(6, 40, generator=g) * 2.0 + 0.25
+    cases = []
+    for dtype in (torch.float32, torch.float16, torch.bfloat16, torch.float64):
+        cases.append(("fnfloat", EveryFloatFunction(), (x.to(dtype), y.to(dtype)), dtype))
+        cases.append(("fnreduce", ReductionKinds(), (x.to(dtype),), dtype))
+        cases.append(("fnprod", ProductRows(), (x[:, :5].contiguous().to(dtype),), dtype))
+    i = torch.randint(-50, 50, (5, 24), generator=g)
+    j = torch.randint(-50, 50, (5, 24), generator=g)
+    cases.append(("fnint", IntegerFunctions(), (i, j), torch.int64))
+    for name, model, inputs, dtype in cases:
+        dname = str(dtype).replace("torch.", "")
+        for cname, kw in (("default", {}), ("streamed", {"max_persistent_row": 4})):
+            if cname == "streamed" and name not in ("fnreduce", "fnprod"):
+                continue
+            sched, params, outs, snaps = reference_run(model.eval(), inputs, kw)
+            path = out_dir / f"{name}__{cname}__{dname}.pt"
+            torch.save({"schedule": kir.dumps(sched), "params": params,
+                        "inputs": [t.clone() for t in inputs], "outputs": outs,
+                        "snapshots": snaps}, path)
+            print(f"{path.name}: {sched.counts()}, {path.stat().st_size / 1024:.1f} KiB", flush=True)
+
+
 #: (schedule stem, model, batch, dtype, variant, sample stride)
 BENCH_CASES = [
     ("encoder-block_b1_s128_float32", "encoder-block", 1, torch.float32, {}, 13),
@@ -179,7 +243,7 @@ def make_bench(out_dir: pathlib.Path, only: str | None) -> None:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--reference", required=True)
-    ap.add_argument("--what", choices=("tiny", "odd", "bench", "all"), default="all")
+    ap.add_argument("--what", choices=("tiny", "odd", "functions", "bench", "all"), default="all")
     ap.add_argument("--only", default=None)
     args = ap.parse_args(argv)
     sys.dont_write_bytecode = True
@@ -189,6 +253,8 @@ def main(argv=None) -> int:
         make_tiny(HERE / "tiny", args.reference)
     if args.what in ("odd", "all"):
         make_odd(HERE / "tiny", args.reference)
+    if args.what in ("functions", "all"):
+        make_functions(HERE / "tiny")
     if args.what in ("bench", "all"):
         make_bench(HERE / "bench", args.only)
     return 0

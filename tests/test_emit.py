@@ -20,7 +20,7 @@ needs_nvcc = pytest.mark.skipif(shutil.which("nvcc") is None and B.nvcc_path() i
 COMPILE_CASES = [s for s in tiny_cases()
                  if s.endswith(("__default__float32", "__streamed__float32", "__default__float16",
                                 "__streamed__bfloat16", "__no_fusion__float32"))
-                 and not s.startswith("block_b8")]
+                 and not s.startswith("block_b8")] + [s for s in tiny_cases() if s.startswith("fn")]
 
 
 def _signature(src: str, symbol: str) -> list[str]:
