@@ -67,7 +67,7 @@ class ClockSampler:
                0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks",
                0x100: "display_clocks"}
 
-    def __init__(self, index: int, period: float = 0.02):
+    def __init__(self, index: int, period: float = 0.005):
         self.index, self.period = index, period
         self.samples: list[int] = []
         self.reasons: set[str] = set()
@@ -316,6 +316,11 @@ def run_reference(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # torchrun pins OMP_NUM_THREADS=1; the baseline is meant to use every host core
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
     steps = min(steps, 60)       # ~0.5 s per forward on 8 cores: stays within a few minutes
     times, cores, sample = cpu_oracle_times(steps, warmup)
