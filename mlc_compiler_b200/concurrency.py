@@ -97,7 +97,6 @@ def assign_streams(deps: list[list[int]], n_streams: int) -> StreamPlan:
     stream = [0] * n
     waits: list[list[int]] = [[] for _ in range(n)]
     signals: set[int] = set()
-    has_succ_on_own_stream = [False] * n
     for j in range(n):
         cands = [stream[p] for p in deps[j] if tail[stream[p]] == p]
         if cands:
@@ -113,8 +112,6 @@ def assign_streams(deps: list[list[int]], n_streams: int) -> StreamPlan:
             if stream[p] != s:
                 waits[j].append(p)
                 signals.add(p)
-        if tail[s] >= 0:
-            has_succ_on_own_stream[tail[s]] = True
         tail[s] = j
     return StreamPlan(stream, waits, signals, n_streams)
 

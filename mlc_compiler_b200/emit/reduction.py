@@ -134,11 +134,6 @@ def varying_steps(k: kir.ReductionKernel) -> set[str]:
     return vec
 
 
-def _expr_varies(e, k, vec) -> bool:
-    col_slots = {i for i, a in enumerate(k.inputs) if a.index.varies_along("col")}
-    return bool((kir.expr_loads(e) & col_slots) or (kir.expr_refs(e) & vec))
-
-
 class _Ctx:
     """Bookkeeping for one kernel emission."""
 
@@ -328,7 +323,6 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
         d.update(vec_vals)
         return d
 
-    step_iter = iter(k.steps)
     pending: list = list(k.steps)
     pos = 0
     for ph in range(n_phases):

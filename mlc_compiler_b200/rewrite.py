@@ -28,7 +28,7 @@ for that producer.
 from __future__ import annotations
 
 from . import kir
-from .kir import Call, Cast, Const, Load, Ref
+from .kir import Call, Cast, Load, Ref
 
 
 class _NoCompose(Exception):
@@ -84,16 +84,6 @@ def _rename(e, prefix: str, slot_map: dict[int, int]):
         return Call(e.fn, tuple(_rename(a, prefix, slot_map) for a in e.args))
     if isinstance(e, Cast):
         return Cast(_rename(e.x, prefix, slot_map), e.dtype)
-    return e
-
-
-def _substitute(e, mapping: dict[int, object]):
-    if isinstance(e, Load):
-        return mapping.get(e.slot, e)
-    if isinstance(e, Call):
-        return Call(e.fn, tuple(_substitute(a, mapping) for a in e.args))
-    if isinstance(e, Cast):
-        return Cast(_substitute(e.x, mapping), e.dtype)
     return e
 
 
