@@ -45,6 +45,11 @@ os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / "gpurun_out" / "mlc_cache"))
 import torch  # noqa: E402
 
 WORKLOAD = "bert-base fp16 b1 s128, one CUDA graph per forward"
+#: dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture
+#: summarised in profiles/micro_kernels_fp16_ncu_full.md (50,343,680 read +
+#: 1,473,024 written while the kernel ran; the remaining 23.7 MB of output were
+#: still dirty in the 126 MB L2 when it ended and are written back afterwards)
+NCU_TRAFFIC = {"micro-gelu:32": 51816704}
 METRIC = "bert_base_fp16_b1_s128_latency"
 
 
@@ -465,7 +470,8 @@ def run_ours(args) -> int:
         micro = micro_roofline(dev, peak, batches=(1, 8, 32), **cfg_kw)
         top = max(micro, key=lambda r: r["alg_bytes"])
         line["roofline"] = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
-                            "frac": top["frac"], "traffic": None,
+                            "frac": top["frac"],
+                            "traffic": NCU_TRAFFIC.get(f"{top['kernel']}:{top['batch']}"),
                             "kernel": f"{top['kernel']} b{top['batch']} fp16",
                             "alg_bytes_per_launch": top["alg_bytes"],
                             "us_per_launch": top["us_per_launch"], "peak_source": peak_kind}
