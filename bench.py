@@ -444,6 +444,12 @@ def run_ours(args) -> int:
     tms = statistics.mean(time_replays(tcm, tdev, max(5, steps // 4), 3, flush))
     thr = replicated_throughput(group, per_gpu, tms, dev)
 
+    # BASELINE configuration 3 beside the headline: GPT-2 small fp16 b1, same timing
+    gcm, gin, gsched = _compiled("gpt2-small", 1, torch.float16, dev, **cfg_kw)
+    gdev = [t.to(dev) for t in gin]
+    gpt_ms = group.max(statistics.mean(time_replays(gcm, gdev, max(10, steps // 4), 3, flush)), dev)
+    del gcm
+
     line = {
         "metric": METRIC, "value": round(ms, 5), "unit": "ms", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 5), "median_ms": round(med, 5),
@@ -459,6 +465,7 @@ def run_ours(args) -> int:
                 "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
         "gpu_launches": cm.generated_launches * steps,
         "clocks": clocks.summary(),
+        "gpt2_small_fp16_b1_ms": round(gpt_ms, 5),
         "timed_region_wall_s": round(wall, 3),
         "replica_throughput": {"model": "bert-base fp16 s128", "global_batch": thr["global_batch"],
                                "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),

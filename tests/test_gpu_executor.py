@@ -151,3 +151,24 @@ def test_forked_graph_is_bitwise_equal_to_the_serial_chain(dev):
         b = forked(*di).clone()
         assert torch.equal(a, b)
     assert [k.name for k in forked.schedule.kernels] == [k.name for k in s.kernels]
+
+
+def test_forked_graph_stays_equal_to_the_serial_chain_under_changing_inputs(dev):
+    """Race check for the parallel branches: 40 replays with fresh inputs, each
+    compared bitwise with the single-stream graph (batch 8 also exercises the
+    forwarded and the transposing kernels)."""
+    from mlc_compiler_b200 import models
+    from mlc_compiler_b200.executor import CompiledModel
+    from mlc_compiler_b200.frontend import load_schedule
+
+    s = load_schedule("bert-base_b8_s128_float16")
+    model, inputs = models.build("bert-base", 8, dtype=torch.float16)
+    serial = CompiledModel(s, model, Config(graph_streams=1, forward_into_copies=False), dev)
+    forked = CompiledModel(s, model, Config(graph_streams=4), dev)
+    g = torch.Generator().manual_seed(3)
+    for _ in range(40):
+        ids = torch.randint(0, 30522, (8, 128), generator=g).to(dev)
+        mask = (torch.rand(8, 128, generator=g) > 0.2).to(torch.float16).to(dev)
+        a = serial(ids, mask).clone()
+        b = forked(ids, mask).clone()
+        assert torch.equal(a, b)
