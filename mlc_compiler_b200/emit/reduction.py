@@ -93,7 +93,8 @@ def plan_geometry(n_rows: int, n_cols: int, operands, cfg, streamed: bool) -> Ge
     P = n_cols // V
     want_np = max(1, int(getattr(cfg, "reduction_packs_per_thread", 4)))
     if streamed:
-        G = min(1024, max(32, pow2_ceil((P + 7) // 8)))
+        # eight packs per lane per pass, at least a warp unless the row is shorter
+        G = min(1024, max(min(32, pow2_ceil(P)), pow2_ceil((P + 7) // 8)))
         G = min(G, 256) if n_rows >= 4 * SM_COUNT else G
     else:
         G = min(1024, pow2_ceil((P + want_np - 1) // want_np))

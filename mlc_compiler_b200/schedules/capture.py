@@ -19,7 +19,7 @@ import torch
 
 
 def configurations():
-    """(file stem, model name, batch, dtype, variant kwargs)."""
+    """(file stem, model name, batch, dtype, variant kwargs[, Config overrides])."""
     out = []
     f16, bf16, f32 = torch.float16, torch.bfloat16, torch.float32
     out.append(("encoder-block_b1_s128_float32", "encoder-block", 1, f32, {}))
@@ -33,6 +33,11 @@ def configurations():
     # the variant the reference itself ships: exact GELU, untied head
     out.append(("gpt2-small-ref_b1_s128_float16", "gpt2-small", 1, f16,
                 {"gelu": "erf", "tied_head": False}))
+    # every row longer than 64 streams (the reference's `--max-row 64` check)
+    out.append(("bert-base-streamed_b1_s128_float16", "bert-base", 1, f16, {},
+                {"max_persistent_row": 64}))
+    out.append(("gpt2-small-streamed_b1_s128_float16", "gpt2-small", 1, f16, {},
+                {"max_persistent_row": 64}))
     for dt in (f16, bf16):
         for b in (1, 8, 32):
             for m in ("micro-layernorm", "micro-softmax", "micro-gelu"):
@@ -54,7 +59,8 @@ def main(argv=None) -> int:
     from mlc_compiler_b200.config import Config
     from mlc_compiler_b200.frontend import capture_schedule, schedule_path
 
-    for stem, name, batch, dtype, variant in configurations():
+    for stem, name, batch, dtype, variant, *rest in configurations():
+        overrides = rest[0] if rest else {}
         stem = stem or models.schedule_name(name, batch, dtype)
         if args.only and args.only not in stem:
             continue
@@ -63,9 +69,10 @@ def main(argv=None) -> int:
             continue
         t0 = time.time()
         model, inputs = models.build(name, batch, dtype=dtype, **variant)
-        sched = capture_schedule(model, inputs, Config())
+        sched = capture_schedule(model, inputs, Config(**overrides))
         sched.meta = {"model": name, "batch": batch, "seq": 128,
-                      "dtype": str(dtype).replace("torch.", ""), "variant": variant}
+                      "dtype": str(dtype).replace("torch.", ""), "variant": variant,
+                      "config": overrides}
         kir.dump(sched, path)
         print(f"{stem}: {len(sched)} kernels {sched.counts()} arena "
               f"{sched.arena_bytes / 1024:.1f} KiB  ({time.time() - t0:.1f}s)", flush=True)

@@ -215,6 +215,10 @@ BENCH_CASES = [
     ("bert-base_b1_s128_float16", "bert-base", 1, torch.float16, {}, 1),
     ("bert-base_b1_s128_float32", "bert-base", 1, torch.float32, {}, 1),
     ("gpt2-small_b1_s128_float16", "gpt2-small", 1, torch.float16, {}, 1009),
+    ("bert-base-streamed_b1_s128_float16", "bert-base", 1, torch.float16, {}, 1,
+     {"max_persistent_row": 64}),
+    ("gpt2-small-streamed_b1_s128_float16", "gpt2-small", 1, torch.float16, {}, 1009,
+     {"max_persistent_row": 64}),
 ]
 
 
@@ -222,11 +226,11 @@ def make_bench(out_dir: pathlib.Path, only: str | None) -> None:
     from mlc_compiler_b200 import models
 
     out_dir.mkdir(parents=True, exist_ok=True)
-    for stem, name, batch, dtype, variant, stride in BENCH_CASES:
+    for stem, name, batch, dtype, variant, stride, *rest in BENCH_CASES:
         if only and only not in stem:
             continue
         model, inputs = models.build(name, batch, dtype=dtype, **variant)
-        sched, _, outs, _ = reference_run(model, inputs, {}, snapshots=False)
+        sched, _, outs, _ = reference_run(model, inputs, rest[0] if rest else {}, snapshots=False)
         with torch.no_grad():
             eager = model(*inputs)
         eager = list(eager) if isinstance(eager, (tuple, list)) else [eager]

@@ -128,7 +128,9 @@ def test_tiny_modules_compile_for_sm_100a(stem, tmp_path):
 
 @needs_nvcc
 @pytest.mark.parametrize("name", ["bert-base_b1_s128_float16", "gpt2-small_b8_s128_bfloat16",
-                                  "micro-gelu_b32_s128_float16", "micro-softmax_b8_s128_float16"])
+                                  "micro-gelu_b32_s128_float16", "micro-softmax_b8_s128_float16",
+                                  "bert-base-streamed_b1_s128_float16",
+                                  "gpt2-small-streamed_b1_s128_float16"])
 def test_benchmark_modules_compile_for_sm_100a(name, tmp_path):
     src = generate_module(load_schedule(name), Config()).source
     log = B.nvcc_cubin(src, tmp_path / "m.cubin", verbose=True)
