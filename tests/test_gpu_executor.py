@@ -172,3 +172,28 @@ def test_forked_graph_stays_equal_to_the_serial_chain_under_changing_inputs(dev)
         a = serial(ids, mask).clone()
         b = forked(ids, mask).clone()
         assert torch.equal(a, b)
+
+
+def test_host_side_failures_are_codes_and_messages_not_faults(dev):
+    """Missing symbol, bad device ordinal, misaligned buffer: each is reported by
+    the library as an error code with a message; the context stays usable."""
+    from mlc_compiler_b200.runtime import BackendError, CudaRuntime, LoadedModule, compile_source
+
+    image = compile_source('extern "C" __global__ void probe(float* p) { p[threadIdx.x] = 1.0f; }')
+    with pytest.raises(BackendError, match="mlcb_module_load"):
+        LoadedModule(image, 99)
+    mod = LoadedModule(image, 0)
+    with pytest.raises(BackendError, match="no_such_kernel"):
+        mod.kernel("no_such_kernel")
+    d = load_tiny("pointwise__default__float32")
+    rt = CudaRuntime(d["schedule"], Config(), dev)
+    k = d["schedule"].generated()[0]
+    bufs = {}
+    for b in set(k.reads()) | set(k.writes()):
+        n = d["schedule"].buffers[b].numel
+        bufs[b] = torch.zeros(n + 1, device=dev)[1:]          # 4-byte, not 16-byte aligned
+    with pytest.raises(BackendError, match="aligned"):
+        rt.launch(k, bufs)
+    # the device is still fine
+    x = torch.ones(32, device=dev)
+    assert float(x.sum()) == 32.0

@@ -203,3 +203,32 @@ def test_batched_models_match_the_oracle_end_to_end(name, batch, dev):
     got = cm(*[t.to(dev) for t in inputs])
     torch.cuda.synchronize()
     assert_close(got, want, "float16", f"{name} b{batch}")
+
+
+def test_indices_beyond_32_bits(dev):
+    """A flat kernel over more than 2^31 elements switches its index arithmetic
+    to 64 bits; checked at the far end of a 4.3 GB buffer."""
+    from mlc_compiler_b200.runtime import CudaRuntime
+
+    n = (1 << 31) + 4096
+    ax = kir.Axis("idx", n, ((n, 1, 1),))
+    k = kir.PointwiseKernel(
+        "k0", (n,), [kir.Operand("x", "x", "float16", kir.IndexMap((ax,)))],
+        [kir.Operand("y", "y", "float16", kir.IndexMap((ax,)))],
+        [("t0", kir.Call("mul", (kir.Load(0), kir.Const(2.0))))], {"y": kir.Ref("t0")}, ["mul"])
+    s = kir.Schedule("big", [k], {"x": kir.BufferSpec("x", (n,), "float16", "input"),
+                                  "y": kir.BufferSpec("y", (n,), "float16", "output")})
+    rt = CudaRuntime(s, Config(), dev)
+    assert "const i64 pack" in rt.source
+    x = torch.empty(n, dtype=torch.float16, device=dev)
+    x[:1 << 20] = 1.5
+    x[-(1 << 20):] = torch.arange(1 << 20, device=dev).to(torch.float16) * 0.25
+    x[1 << 30] = 3.0
+    y = torch.zeros(n, dtype=torch.float16, device=dev)
+    rt.launch(k, {"x": x, "y": y})
+    torch.cuda.synchronize()
+    assert torch.equal(y[-(1 << 20):], x[-(1 << 20):] * 2)
+    assert torch.equal(y[:1 << 20], x[:1 << 20] * 2)
+    assert float(y[1 << 30]) == 6.0
+    del x, y
+    torch.cuda.empty_cache()
