@@ -74,7 +74,7 @@ MLCB_PLAIN_ELEM(bool)
 
 // ---------------------------------------------------------------------------
 // packed global access: W consecutive elements, W * sizeof(T) bytes, aligned to
-// min(16, W * sizeof(T)).  The emitter proves the alignment from the index map
+// min(32, W * sizeof(T)).  The emitter proves the alignment from the index map
 // before it asks for a width.
 // ---------------------------------------------------------------------------
 template <int BYTES> struct mlcb_word;
@@ -83,11 +83,29 @@ template <> struct mlcb_word<2>  { typedef unsigned short type; };
 template <> struct mlcb_word<4>  { typedef unsigned int   type; };
 template <> struct mlcb_word<8>  { typedef uint2          type; };
 template <> struct mlcb_word<16> { typedef uint4          type; };
+// 256-bit global accesses are new with sm_100 (ld/st.global.v4.b64): one
+// instruction moves 32 bytes per lane, 1 KB per warp.
+struct alignas(32) mlcb_u256 { unsigned long long x[4]; };
+template <> struct mlcb_word<32> { typedef mlcb_u256      type; };
+
+template <typename W> __device__ __forceinline__ W mlcb_ld_word(const W* p) { return *p; }
+template <typename W> __device__ __forceinline__ void mlcb_st_word(W* p, const W& v) { *p = v; }
+template <> __device__ __forceinline__ mlcb_u256 mlcb_ld_word<mlcb_u256>(const mlcb_u256* p) {
+    mlcb_u256 v;
+    asm volatile("ld.global.v4.u64 {%0, %1, %2, %3}, [%4];"
+                 : "=l"(v.x[0]), "=l"(v.x[1]), "=l"(v.x[2]), "=l"(v.x[3]) : "l"(p));
+    return v;
+}
+template <> __device__ __forceinline__ void mlcb_st_word<mlcb_u256>(mlcb_u256* p, const mlcb_u256& v) {
+    asm volatile("st.global.v4.u64 [%4], {%0, %1, %2, %3};"
+                 :: "l"(v.x[0]), "l"(v.x[1]), "l"(v.x[2]), "l"(v.x[3]), "l"(p) : "memory");
+}
 
 template <typename T, int W>
 struct mlcb_pack {
     static constexpr int BYTES = W * (int)sizeof(T);
-    static constexpr int CHUNK = BYTES > 16 ? 16 : BYTES;   // bytes per instruction
+    // bytes per instruction: 32 when the pack is a whole number of 256-bit words
+    static constexpr int CHUNK = (BYTES % 32 == 0) ? 32 : (BYTES > 16 ? 16 : BYTES);
     static constexpr int N = BYTES / CHUNK;
     typedef typename mlcb_word<CHUNK>::type word;
     union { word w[N]; T e[W]; };
@@ -101,7 +119,7 @@ __device__ __forceinline__ void mlcb_load(const T* __restrict__ p,
     typedef typename mlcb_pack<T, W>::word word;
     const word* q = reinterpret_cast<const word*>(p);
 #pragma unroll
-    for (int i = 0; i < mlcb_pack<T, W>::N; ++i) u.w[i] = q[i];
+    for (int i = 0; i < mlcb_pack<T, W>::N; ++i) u.w[i] = mlcb_ld_word(q + i);
 #pragma unroll
     for (int i = 0; i < W; ++i) dst[i] = mlcb_elem<T>::get(u.e[i]);
 }
@@ -161,7 +179,7 @@ __device__ __forceinline__ void mlcb_store(T* __restrict__ p,
     mlcb_packer<T, W>::run(u, src);
     word* q = reinterpret_cast<word*>(p);
 #pragma unroll
-    for (int i = 0; i < mlcb_pack<T, W>::N; ++i) q[i] = u.w[i];
+    for (int i = 0; i < mlcb_pack<T, W>::N; ++i) mlcb_st_word(q + i, u.w[i]);
 }
 
 template <typename T, int W, int V>

@@ -79,6 +79,12 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
     tile = plan_tile(k, V)
     if tile is not None:
         return _emit_tiled(k, cfg, name, V, tile)
+    # large streaming kernels use 256-bit accesses (two 128-bit packs per thread)
+    wide = int(getattr(cfg, "wide_access_bytes", 0) or 0)
+    if wide and algorithmic_bytes(k.inputs, k.outputs, numel) >= wide:
+        V2 = pick_vector(operands, numel, cap_bytes=32)
+        if V2 > V and all(classify(a.index, "idx", V2).width == V2 for a in operands):
+            V = V2
     packs = numel // V
     extents = [numel] + [a.index.bounds()[1] + 1 for a in operands]
     it = "i64" if needs_64bit(*extents) else "int"

@@ -217,8 +217,8 @@ class BoundLaunch:
 
     def _set(self, tensors) -> None:
         for t in tensors:
-            if t.data_ptr() % 16 != 0:
-                raise BackendError(f"{self.name}: buffer at {t.data_ptr():#x} is not 16-byte "
+            if t.data_ptr() % 32 != 0:
+                raise BackendError(f"{self.name}: buffer at {t.data_ptr():#x} is not 32-byte "
                                    "aligned; packed accesses were proven from aligned bases")
         self.tensors = tensors
         self.nptrs = len(tensors)

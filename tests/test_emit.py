@@ -143,3 +143,14 @@ def test_dependent_launch_variant_compiles(tmp_path):
                           Config(dependent_launch=True)).source
     assert "#define MLCB_PDL 1" in src
     B.nvcc_cubin(src, tmp_path / "m.cubin")
+
+
+def test_large_streaming_kernels_use_256_bit_accesses():
+    """75 MB bias+GELU+residual: 16 halves per thread, one ld.global.v4.b64 each;
+    the 2 MB batch-1 shape keeps 128-bit packs (more threads, lower latency)."""
+    big = generate_module(load_schedule("micro-gelu_b32_s128_float16"), Config())
+    assert big.launch["k0"].vector == 16 and "mlcb_load<__half, 16>" in big.source
+    small = generate_module(load_schedule("micro-gelu_b1_s128_float16"), Config())
+    assert small.launch["k0"].vector == 8
+    off = generate_module(load_schedule("micro-gelu_b32_s128_float16"), Config(wide_access_bytes=0))
+    assert off.launch["k0"].vector == 8
