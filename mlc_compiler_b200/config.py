@@ -54,6 +54,8 @@ class Config:
     #: pointwise kernels that move at least this many bytes use 256-bit global
     #: accesses (sm_100 ``ld/st.global.v4.b64``) when every operand allows it; 0 = never
     wide_access_bytes: int = 8 << 20
+    #: same for persistent row reductions (0 = never; measured no better than 128-bit)
+    wide_reduction_bytes: int = 0
     #: fold a pointwise producer into the pointwise kernels that only re-read it at
     #: another index (bias add + head-layout copy at batch > 1); bit-identical
     forward_into_copies: bool = True

@@ -88,8 +88,14 @@ class Geometry:
         return self.G > 32
 
 
-def plan_geometry(n_rows: int, n_cols: int, operands, cfg, streamed: bool) -> Geometry:
+def plan_geometry(n_rows: int, n_cols: int, operands, cfg, streamed: bool,
+                  alg_bytes: int = 0) -> Geometry:
     V = pick_vector(operands, n_cols)
+    wide = int(getattr(cfg, "wide_reduction_bytes", 0) or 0)
+    if wide and alg_bytes >= wide and not streamed:
+        V2 = pick_vector(operands, n_cols, cap_bytes=32)
+        if V2 > V and all(classify(a.index, "col", V2).width == V2 for a in operands):
+            V = V2
     P = n_cols // V
     want_np = max(1, int(getattr(cfg, "reduction_packs_per_thread", 4)))
     if streamed:
@@ -242,7 +248,8 @@ def _col_off(a, var: str) -> str:
 def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchSpec]:
     operands = [a for a in k.inputs if a.index.varies_along("col")] + [
         a for a in k.outputs if a.name not in k.row_outputs]
-    geo = plan_geometry(k.n_rows, k.n_cols, operands or k.inputs + k.outputs, cfg, False)
+    geo = plan_geometry(k.n_rows, k.n_cols, operands or k.inputs + k.outputs, cfg, False,
+                        algorithmic_bytes(k.inputs, k.outputs, k.n_rows * k.n_cols))
     V, G, NP = geo.V, geo.G, geo.NP
     extents = [k.n_rows * max(1, k.n_cols)] + [a.index.bounds()[1] + 1
                                                for a in k.inputs + k.outputs]
