@@ -46,20 +46,30 @@ def _source_text(schedule, cfg) -> str:
     return _generate_module(schedule, cfg).source
 
 
-def install() -> None:
-    """Route the reference's generated-kernel path through this backend."""
+def install(native_executor: bool = False) -> None:
+    """Route the reference's generated-kernel path through this backend.
+
+    By default only the kernel runtime is swapped and the reference's own
+    executor keeps driving it (same single-stream graph as before).  With
+    ``native_executor=True`` ``mlc.compile`` additionally returns this package's
+    executor for CUDA devices, which captures the schedule with parallel graph
+    branches and folds producers into copies; ``backend="torch"`` and CPU
+    devices still get the reference's executor and interpreter."""
     reference()
     from .runtime import CudaRuntime
 
     ex = importlib.import_module("mlc.runtime.executor")
     tr = importlib.import_module("mlc.runtime.triton_runtime")
     tb = importlib.import_module("mlc.codegen.triton_backend")
+    api = importlib.import_module("mlc.api")
     if not _saved:
         _saved.update(select_backend=ex.select_backend, TritonRuntime=tr.TritonRuntime,
-                      generate_module=tb.generate_module)
+                      generate_module=tb.generate_module, CompiledModel=api.CompiledModel)
     ex.select_backend = _select_backend
     tr.TritonRuntime = CudaRuntime
     tb.generate_module = _source_text
+    api.CompiledModel = _native_factory(_saved["CompiledModel"]) if native_executor \
+        else _saved["CompiledModel"]
 
 
 def uninstall() -> None:
@@ -71,7 +81,79 @@ def uninstall() -> None:
     ex.select_backend = _saved["select_backend"]
     tr.TritonRuntime = _saved["TritonRuntime"]
     tb.generate_module = _saved["generate_module"]
+    importlib.import_module("mlc.api").CompiledModel = _saved["CompiledModel"]
     _saved.clear()
+
+
+def _native_factory(reference_executor):
+    """A stand-in for the reference's ``CompiledModel(graph, schedule, cfg, device)``
+    constructor (``mlc/api.py:33``) that builds this package's executor."""
+
+    def make(graph, schedule, cfg, device):
+        device = torch.device(device)
+        if _select_backend(cfg, device) == "torch":
+            return reference_executor(graph, schedule, cfg, device)
+        return NativeCompiledModel(graph, schedule, cfg, device)
+
+    return make
+
+
+class NativeCompiledModel:
+    """This package's executor behind the reference's ``CompiledModel`` surface:
+    ``graph``, ``schedule`` (the reference's own object), ``cfg``, ``device``,
+    ``backend``, ``__call__``, ``forward``, ``source()``, ``source_path()``,
+    ``profile_kernels()``; outputs are re-assembled with the exporter's pytree
+    spec exactly as ``_collect`` does (``mlc/runtime/executor.py:244-261``)."""
+
+    def __init__(self, graph, schedule, cfg, device) -> None:
+        from . import kir
+        from .executor import CompiledModel
+
+        self.graph, self.schedule, self.cfg = graph, schedule, cfg
+        self.device = torch.device(device)
+        self.backend = "cuda"
+        ours = Config()
+        for f in ours.__dataclass_fields__:
+            if hasattr(cfg, f):
+                setattr(ours, f, getattr(cfg, f))
+        params = {v.buffer.name: graph.param_tensors[v.name] for v in graph.params}
+        self._impl = CompiledModel(kir.from_reference(schedule), params, ours, self.device)
+        self.params = self._impl.params
+        self._out_spec = graph.meta.get("out_spec")
+
+    def _shape(self, out):
+        if self._out_spec is None:
+            return out
+        from torch.utils._pytree import tree_unflatten
+
+        flat = list(out) if isinstance(out, tuple) else [out]
+        try:
+            return tree_unflatten(flat, self._out_spec)
+        except Exception:
+            return out
+
+    def __call__(self, *inputs):
+        return self._shape(self._impl(*inputs))
+
+    def forward(self, *inputs):
+        return self._shape(self._impl.forward(*inputs))
+
+    def profile_kernels(self, inputs, iters: int = 20):
+        return self._impl.profile_kernels(inputs, iters)
+
+    def source(self) -> str:
+        return self._impl.source()
+
+    def source_path(self):
+        return self._impl.source_path()
+
+    @property
+    def executed_schedule(self):
+        return self._impl.executed_schedule
+
+    def __repr__(self) -> str:  # pragma: no cover
+        return (f"CompiledModel({self.graph.name}, {len(self.schedule)} kernels, "
+                f"backend={self.backend}, device={self.device})")
 
 
 def compile(model, example_inputs, config: Config | None = None, device=None):

@@ -88,3 +88,24 @@ def test_frontend_bridge_captures_into_this_ir(installed):
     s = capture_schedule(M(), (torch.randn(3, 16),), Config())
     assert isinstance(s, kir.Schedule) and s.counts() == {"reduction": 1}
     assert kir.dumps(kir.loads(kir.dumps(s))) == kir.dumps(s)
+
+
+def test_native_executor_is_opt_in_and_leaves_the_interpreter_alone(installed):
+    import mlc
+    import mlc.api as api
+    from mlc.config import Config
+
+    reference_cls = api.CompiledModel
+    installed.install(native_executor=True)
+    assert api.CompiledModel is not reference_cls
+
+    class M(torch.nn.Module):
+        def forward(self, x):
+            return (x * 2.0).softmax(-1)
+
+    x = torch.randn(3, 16)
+    c = mlc.compile(M(), (x,), Config(backend="torch", cuda_graphs=False), device="cpu")
+    assert isinstance(c, reference_cls)                 # CPU / torch backend: untouched
+    torch.testing.assert_close(c(x), (x * 2.0).softmax(-1))
+    installed.install()                                  # default: reference executor again
+    assert api.CompiledModel is reference_cls
