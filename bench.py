@@ -443,6 +443,14 @@ def run_ours(args) -> int:
     tdev = [t.to(dev) for t in tin]
     tms = statistics.mean(time_replays(tcm, tdev, max(5, steps // 4), 3, flush))
     thr = replicated_throughput(group, per_gpu, tms, dev)
+    # and with the per-GPU batch held at 32 (work grows with the replica count)
+    if per_gpu == 32:
+        weak = dict(thr)
+    else:
+        wcm, win, _ = _compiled("bert-base", 32, torch.float16, dev, **cfg_kw)
+        wms = statistics.mean(time_replays(wcm, [t.to(dev) for t in win], max(5, steps // 4), 3, flush))
+        weak = replicated_throughput(group, 32, wms, dev)
+        del wcm
 
     # BASELINE configuration 3 beside the headline: GPT-2 small fp16 b1, same timing
     gcm, gin, gsched = _compiled("gpt2-small", 1, torch.float16, dev, **cfg_kw)
@@ -470,7 +478,11 @@ def run_ours(args) -> int:
         "replica_throughput": {"model": "bert-base fp16 s128", "global_batch": thr["global_batch"],
                                "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
                                "ms_per_forward": round(thr["ms_per_forward"], 4),
-                               "arena_mb_per_gpu": round(tsched.arena_bytes / 2**20, 2)},
+                               "arena_mb_per_gpu": round(tsched.arena_bytes / 2**20, 2),
+                               "fixed_per_gpu_batch_32": {
+                                   "global_batch": weak["global_batch"],
+                                   "seq_per_s": round(weak["seq_per_s"], 1),
+                                   "ms_per_forward": round(weak["ms_per_forward"], 4)}},
     }
 
     if rank == 0:
