@@ -217,7 +217,9 @@ def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64,
                     if n not in bufs:
                         bufs[n] = torch.empty(sched.buffers[n].numel, device=dev,
                                               dtype=getattr(torch, sched.buffers[n].dtype))
-                bound.append(rt.bind(k, bufs)[0])
+                # consecutive generated kernels on one stream: what the executor's
+                # "chain" policy launches programmatically
+                bound.append(rt.bind(k, bufs, 1 if (rt.chain or rt.flags) else 0)[0])
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):

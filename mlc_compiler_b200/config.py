@@ -48,9 +48,9 @@ class Config:
     #: kernels whose every output is fp16/bf16 may use SFU-based exp/tanh/erf and
     #: division (error ~1e-6, below half-precision resolution); fp32 kernels never do
     narrow_fast_math: bool = True
-    #: launch generated kernels with programmatic stream serialisation and emit
-    #: the matching grid-dependency instructions
-    dependent_launch: bool = False
+    #: programmatic dependent launch of generated kernels: False, True (every
+    #: launch) or "chain" (only behind another generated kernel on the same stream)
+    dependent_launch: bool | str = "chain"
     #: pointwise kernels that move at least this many bytes use 256-bit global
     #: accesses (sm_100 ``ld/st.global.v4.b64``) when every operand allows it; 0 = never
     wide_access_bytes: int = 8 << 20

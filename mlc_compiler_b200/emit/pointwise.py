@@ -49,6 +49,14 @@ def algorithmic_bytes(inputs, outputs, iter_numel: int) -> int:
     return total
 
 
+def single_wave(grid: int, block: int, sms: int = 148) -> bool:
+    """Whether every CTA of the launch can be resident at once (1024 threads per
+    SM assumed).  Only such launches release their dependents early: a dependent
+    grid that becomes resident while later waves of its predecessor are still
+    waiting for SM slots takes those slots and just sits at its wait."""
+    return grid * block <= sms * 1024
+
+
 def pick_vector(operands, numel: int, cap_bytes: int = 16) -> int:
     smallest = min((kir.ITEMSIZE[a.dtype] for a in operands), default=4)
     v = max(1, cap_bytes // smallest)
@@ -154,7 +162,8 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
         else:
             need_idx = True
 
-    L.append("    MLCB_GRID_TRIGGER();")
+    if single_wave(grid, block):
+        L.append("    MLCB_GRID_TRIGGER();")
     L.append("#pragma unroll")
     L.append(f"    for (int j = 0; j < {V}; ++j) {{")
     if need_idx:
@@ -361,7 +370,8 @@ def _emit_tiled(k: kir.PointwiseKernel, cfg, name: str, V: int, tile: Tile) -> t
                 L.append(f"    {rt} g{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + "
                          f"({render_offset(a.index, {'idx': 'base_idx'})}), g{i});  // {a.name}: along r only")
                 loads[i] = X.Val(f"g{i}[i]", vdt)
-    L.append("    MLCB_GRID_TRIGGER();")
+    if single_wave(grid, block):
+        L.append("    MLCB_GRID_TRIGGER();")
     L.append("#pragma unroll")
     L.append(f"    for (int i = 0; i < {V}; ++i) {{")
     L.append(f"        const {it} i0 = base_idx + i * {o_r};")

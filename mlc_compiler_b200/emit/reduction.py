@@ -38,7 +38,7 @@ from ..kir import Bind, Reduce
 from . import expr as X
 from .indexing import (Access, check_bounds, classify, needs_64bit, pow2_ceil,
                        render_offset)
-from .pointwise import LaunchSpec, algorithmic_bytes, pick_vector, store_code
+from .pointwise import LaunchSpec, algorithmic_bytes, pick_vector, single_wave, store_code
 
 _OP = {"sum": "mlcb_op_sum", "prod": "mlcb_op_prod", "max": "mlcb_op_max", "min": "mlcb_op_min"}
 
@@ -455,7 +455,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
         c.emit("    }")
         if red is not None:
             _finish_reduce(c, red, acc_dt, rdt, reduces.index(red))
-        if ph == 0:
+        if ph == 0 and single_wave(geo.grid, geo.block):
             c.emit("    MLCB_GRID_TRIGGER();")
 
     _row_stores(c, loads)
@@ -595,7 +595,8 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
     scalar_in = _scalar_loads(c)
     _row_offsets(c, k.inputs, "in")
     _row_offsets(c, k.outputs, "out")
-    c.emit("    MLCB_GRID_TRIGGER();")
+    if single_wave(geo.grid, geo.block):
+        c.emit("    MLCB_GRID_TRIGGER();")
 
     acc_in = {i: classify(a.index, "col", V) for i, a in enumerate(k.inputs)
               if a.index.varies_along("col")}

@@ -234,8 +234,15 @@ class CompiledModel:
                 plan.append(("cuda", LaunchRun(self._module.lib, list(run))))
                 run.clear()
 
-        for k in self._exec.kernels:
+        # "chain": a launch is programmatic only when the kernel enqueued just
+        # before it on the same stream is a generated one (a library kernel
+        # never releases its dependents early)
+        chain = getattr(self.cfg, "dependent_launch", False) == "chain"
+        tail_generated: dict[int, bool] = {}
+        for j, k in enumerate(self._exec.kernels):
+            lane = self._streams.stream[j] if self._streams is not None else 0
             if isinstance(k, kir.ExternKernel):
+                tail_generated[lane] = False
                 flush()
                 b = bind_extern(k, buffers)
                 self._bound[k.name] = ("extern", b)
@@ -243,8 +250,9 @@ class CompiledModel:
                 plan.append(("extern", b))
             elif isinstance(k, (kir.PointwiseKernel, kir.ReductionKernel)):
                 flags = None
-                if getattr(self.cfg, "dependent_launch", False) == "chain" and not run:
-                    flags = 0      # first of a run: its predecessor is a library kernel
+                if chain:
+                    flags = 1 if tail_generated.get(lane, False) else 0
+                tail_generated[lane] = True
                 fn = self._module.bind(k, buffers, flags)[0]
                 self._bound[k.name] = ("cuda", fn)
                 self._per_kernel.append(("cuda", fn))

@@ -282,7 +282,10 @@ class CudaRuntime:
             torch.cuda.current_stream()  # makes sure the primary context exists
             self.loaded = LoadedModule(compile_source(self.source), index)
         self.lib = self.loaded.lib
-        self.flags = 1 if getattr(cfg, "dependent_launch", False) else 0
+        # "chain" is resolved per launch by an executor that knows the stream order;
+        # a host that binds kernels one by one gets plain launches
+        self.flags = 1 if getattr(cfg, "dependent_launch", False) is True else 0
+        self.chain = getattr(cfg, "dependent_launch", False) == "chain"
 
     @staticmethod
     def _is_extern(k) -> bool:
@@ -300,9 +303,10 @@ class CudaRuntime:
             raise TypeError("extern kernels do not go through the CUDA runtime")
         spec = self.generated.launch[k.name]
         tensors = tuple(buffers[n] for n in self._buffer_names(k))
+        if flags is None:
+            flags = self.flags
         fn = BoundLaunch(self.lib, self.loaded.kernel(self.generated.symbol[k.name]), k.name,
-                         spec.grid, spec.block, spec.smem,
-                         self.flags if flags is None else flags, tensors)
+                         spec.grid, spec.block, spec.smem, flags, tensors)
         return fn, spec.grid, tensors, {}
 
     def launch(self, k, buffers: dict[str, torch.Tensor]) -> None:
