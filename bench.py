@@ -40,7 +40,7 @@ import time
 
 ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
-os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / "gpurun_out" / "mlc_cache"))
+os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / ".mlc_cache"))
 
 import torch  # noqa: E402
 

@@ -7,7 +7,7 @@ import pytest
 ROOT = pathlib.Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "oracle"))
-os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / "gpurun_out" / "mlc_cache"))
+os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / ".mlc_cache"))
 
 GOLDEN = ROOT / "tests" / "golden"
 

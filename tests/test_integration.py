@@ -1,6 +1,6 @@
 """Drop-in installation into the reference, exercised where a checkout of the
-reference is present (its path in $MLC_REFERENCE, default /root/reference);
-skipped elsewhere.  CPU only: it checks routing and source generation, not
+reference is present (its path in $MLC_REFERENCE, default: a ``reference``
+directory beside this repository); skipped elsewhere.  CPU only: it checks routing and source generation, not
 execution."""
 
 import os
@@ -10,7 +10,8 @@ import sys
 import pytest
 import torch
 
-REF = pathlib.Path(os.environ.get("MLC_REFERENCE", "/root/reference"))
+REF = pathlib.Path(os.environ.get(
+    "MLC_REFERENCE", pathlib.Path(__file__).resolve().parent.parent.parent / "reference"))
 pytestmark = pytest.mark.skipif(not (REF / "mlc" / "api.py").exists(),
                                 reason="reference checkout not present")
 
