@@ -42,7 +42,10 @@ class Config:
 
     # -- CUDA backend only -----------------------------------------------------
     #: packs of 128 bits each thread of a persistent row reduction aims to own
-    reduction_packs_per_thread: int = 4
+    reduction_packs_per_thread: int = 2
+    #: a row goes to a whole CTA (shared-memory hop) only when a warp would need
+    #: more than this many packs per lane
+    reduction_max_packs: int = 8
     #: force the number of threads that share one row (0 = choose)
     reduction_group: int = 0
     #: kernels whose every output is fp16/bf16 may use SFU-based exp/tanh/erf and

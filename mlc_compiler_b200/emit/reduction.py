@@ -97,13 +97,19 @@ def plan_geometry(n_rows: int, n_cols: int, operands, cfg, streamed: bool,
         if V2 > V and all(classify(a.index, "col", V2).width == V2 for a in operands):
             V = V2
     P = n_cols // V
-    want_np = max(1, int(getattr(cfg, "reduction_packs_per_thread", 4)))
+    want_np = max(1, int(getattr(cfg, "reduction_packs_per_thread", 2)))
     if streamed:
         # eight packs per lane per pass, at least a warp unless the row is shorter
         G = min(1024, max(min(32, pow2_ceil(P)), pow2_ceil((P + 7) // 8)))
         G = min(G, 256) if n_rows >= 4 * SM_COUNT else G
     else:
-        G = min(1024, pow2_ceil((P + want_np - 1) // want_np))
+        # Prefer a slice of one warp (no shared memory, no barrier) with about
+        # want_np packs per lane; go to a CTA per row only when a warp would need
+        # more than max_np packs per lane.
+        max_np = max(want_np, int(getattr(cfg, "reduction_max_packs", 8)))
+        G = min(32, pow2_ceil((P + want_np - 1) // want_np))
+        if (P + G - 1) // G > max_np:
+            G = min(1024, pow2_ceil((P + 3) // 4))
         # small problems: spread each row over more lanes until the machine is
         # covered, as long as every lane still has a pack
         while G < 1024 and G * 2 <= pow2_ceil(P) and n_rows * G < SM_COUNT * 128:
