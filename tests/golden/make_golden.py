@@ -215,6 +215,12 @@ BENCH_CASES = [
     ("bert-base_b1_s128_float16", "bert-base", 1, torch.float16, {}, 1),
     ("bert-base_b1_s128_float32", "bert-base", 1, torch.float32, {}, 1),
     ("gpt2-small_b1_s128_float16", "gpt2-small", 1, torch.float16, {}, 1009),
+    ("bert-base_b1_s128_bfloat16", "bert-base", 1, torch.bfloat16, {}, 1),
+    ("gpt2-small_b1_s128_bfloat16", "gpt2-small", 1, torch.bfloat16, {}, 1009),
+    ("bert-base_b4_s128_float16", "bert-base", 4, torch.float16, {}, 1),
+    ("gpt2-small_b4_s128_float16", "gpt2-small", 4, torch.float16, {}, 4001),
+    ("gpt2-small-ref_b1_s128_float16", "gpt2-small", 1, torch.float16,
+     {"gelu": "erf", "tied_head": False}, 1009),
     ("bert-base-streamed_b1_s128_float16", "bert-base", 1, torch.float16, {}, 1,
      {"max_persistent_row": 64}),
     ("gpt2-small-streamed_b1_s128_float16", "gpt2-small", 1, torch.float16, {}, 1009,

@@ -90,7 +90,16 @@ def test_benchmark_configurations_match_the_reference_samples(stem, dev):
     outs = list(out) if isinstance(out, tuple) else [out]
     torch.cuda.synchronize()
     for got, want in zip(outs, g["samples"]):
-        assert_close(got.reshape(-1)[::g["stride"]], want, m["dtype"], stem)
+        if m["dtype"] == "bfloat16" and len(s) > 10:
+            # Whole bf16 models: the golden ran its 100 matmuls on the CPU, this run on
+            # cuBLAS, and bf16 keeps 8 bits, so the outputs drift apart by a few bf16
+            # ulps of the largest activations whatever the fused kernels do.  Bar here:
+            # 5e-2 abs/rel; the fused kernels themselves are held to 1e-2 on identical
+            # inputs by test_every_kernel_of_a_model_matches_the_oracle_on_the_same_inputs.
+            g_, w_ = got.reshape(-1)[::g["stride"]].float().cpu(), want.float()
+            assert bool(((g_ - w_).abs() <= 5e-2 + 5e-2 * w_.abs()).all()), stem
+        else:
+            assert_close(got.reshape(-1)[::g["stride"]], want, m["dtype"], stem)
 
 
 @pytest.mark.parametrize("name", ["micro-layernorm", "micro-softmax", "micro-gelu"])
@@ -232,3 +241,39 @@ def test_indices_beyond_32_bits(dev):
     assert float(y[1 << 30]) == 6.0
     del x, y
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("stem", ["bert-base_b1_s128_bfloat16", "gpt2-small_b1_s128_bfloat16",
+                                  "bert-base_b1_s128_float16", "gpt2-small_b4_s128_float16",
+                                  "bert-base_b1_s128_float32"])
+def test_every_kernel_of_a_model_matches_the_oracle_on_the_same_inputs(stem, dev):
+    """Walk a whole model on the GPU and, at every generated kernel, hand the
+    oracle exactly the buffers the kernel read (cuBLAS outputs included): each
+    fused kernel is then compared on identical inputs, so matmul rounding
+    differences between CPU and GPU cannot blur the comparison.  1e-2 abs/rel
+    for fp16/bf16, 1e-4 for fp32."""
+    from mlc_compiler_b200.executor import CompiledModel, run_bound_extern
+
+    s = load_schedule(stem)
+    m = s.meta
+    model, inputs = models.build(m["model"], m["batch"], dtype=kir.torch_dtype(m["dtype"]),
+                                 **m.get("variant", {}))
+    cm = CompiledModel(s, model, Config(cuda_graphs=False), dev)
+    buffers = cm._resident_buffers([t.to(dev) for t in inputs])
+    cm._plan = cm._build_plan(buffers)
+    checked = 0
+    for k in cm.executed_schedule.kernels:
+        kind, bound = cm._bound[k.name]
+        if kind == "extern":
+            run_bound_extern(bound)
+            continue
+        cpu = {b: buffers[b].detach().cpu().clone() for b in set(k.reads())}
+        for b in k.writes():
+            cpu[b] = torch.zeros_like(buffers[b], device="cpu")
+        bound[bound.grid]()
+        torch.cuda.synchronize()
+        oracle.run_kernel(k, cpu)
+        for a in k.outputs:
+            assert_close(buffers[a.buffer], cpu[a.buffer], a.dtype, f"{stem} {k.name} ({k.summary()})")
+        checked += 1
+    assert checked == cm.generated_launches
