@@ -96,6 +96,10 @@ class Val:
     dim: bool = True
     #: varies along the column axis of a reduction kernel (unused by pointwise)
     varies: bool = False
+    #: ``(fp32 code, narrow dtype)`` when ``code`` is that fp32 expression rounded
+    #: to fp16/bf16 (possibly widened again): a store to the same narrow dtype
+    #: can take the unrounded expression, because storing rounds identically
+    unrounded: tuple[str, str] | None = None
 
 
 def is_float(dt: str) -> bool:
@@ -340,7 +344,14 @@ def render(e: Expr, loads: list[Val], refs: dict[str, Val]) -> Val:
         return const_val(e)
     if isinstance(e, Cast):
         x = render(e.x, loads, refs)
-        return Val(convert(x.code, x.dtype, e.dtype), e.dtype, x.dim, x.varies)
+        unrounded = None
+        if e.dtype in kir.NARROW_FLOATS and x.dtype == "float32":
+            unrounded = (x.code, e.dtype)
+        elif e.dtype == "float32" and x.dtype in kir.NARROW_FLOATS:
+            unrounded = x.unrounded            # exact widening of a rounded value
+        elif e.dtype == x.dtype:
+            unrounded = x.unrounded
+        return Val(convert(x.code, x.dtype, e.dtype), e.dtype, x.dim, x.varies, unrounded)
     if isinstance(e, Call):
         if e.fn == "div" and isinstance(e.args[1], Const) and _is_pow2(e.args[1].value):
             # x / 2^k == x * 2^-k in IEEE arithmetic, and a multiply is one

@@ -203,27 +203,15 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
 def store_code(v: X.Val, out_dtype: str) -> str:
     """Register value handed to a store of ``out_dtype``.  The store itself
     rounds a float register to fp16/bf16, so a float32 (or already narrow)
-    value is passed through rather than rounded twice."""
-    if out_dtype in kir.NARROW_FLOATS and v.dtype in ("float32", out_dtype):
-        return _strip_round(v.code, out_dtype)
+    value is passed through rather than rounded twice, and a value that is
+    known to be ``round(x)`` to this same dtype is stored as ``x``."""
     if out_dtype in kir.NARROW_FLOATS:
+        if v.unrounded is not None and v.unrounded[1] == out_dtype:
+            return v.unrounded[0]
+        if v.dtype in ("float32", out_dtype):
+            return v.code
         return X.convert(v.code, v.dtype, "float32")
     return X.convert(v.code, v.dtype, out_dtype)
-
-
-def _strip_round(code: str, dtype: str) -> str:
-    """``mlcb_rn_f16(x)`` handed to an fp16 store is ``x``: the store rounds the
-    same way (likewise bf16).  Only a call wrapping the whole expression counts."""
-    head = "mlcb_rn_f16(" if dtype == "float16" else "mlcb_rn_bf16("
-    if not (code.startswith(head) and code.endswith(")")):
-        return code
-    depth = 0
-    for i, ch in enumerate(code[len(head) - 1:]):
-        depth += ch == "("
-        depth -= ch == ")"
-        if depth == 0:
-            return code[len(head):-1] if i == len(code) - len(head) else code
-    return code
 
 
 # --------------------------------------------------------------------------
