@@ -335,8 +335,9 @@ def run_reference(args) -> int:
     line = {
         "impl": "reference", "metric": METRIC, "value": round(ms, 4), "unit": "ms",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
-        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": {"workload": WORKLOAD, "device": "cpu",
+                                        "accumulate": "f32",
                                         "note": "reference torch backend restated (oracle port), "
                                                 "all host threads"},
         "cpu_baseline": {"value": round(ms, 4), "unit": "ms", "cores": cores, "kind": "port",
@@ -465,7 +466,8 @@ def run_ours(args) -> int:
         "warmup": warmup, "ms_per_step": round(ms, 5), "median_ms": round(med, 5),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "kernels": len(sched), "generated": cm.generated_launches,
+        "config": {"workload": WORKLOAD, "accumulate": "f32", "kernels": len(sched),
+                   "generated": cm.generated_launches,
                    "arena_kib": round(sched.arena_bytes / 1024, 1),
                    "l2": "flushed between steps (256 MiB write)",
                    "graph_streams": cm.cfg.graph_streams, "dependent_launch": cm.cfg.dependent_launch,
