@@ -112,3 +112,31 @@ def prebuild(source: str) -> pathlib.Path:
     if not out.exists():
         nvcc_cubin(source, out)
     return out
+
+
+EXAMPLE = CSRC / "examples" / "bert-base_b8_s128_float16.cu"
+
+
+def example_source() -> str:
+    """The translation unit the executor compiles for BERT-base fp16 at batch 8
+    (after producer forwarding): every kernel family in one readable file.  A
+    copy is kept under ``csrc/examples`` so that the generated CUDA can be read
+    without running anything; ``write_example`` refreshes it and a test keeps it
+    honest."""
+    from .config import Config
+    from .emit import generate_module
+    from .frontend import load_schedule
+    from .rewrite import forward_into_consumers
+
+    sched = forward_into_consumers(load_schedule("bert-base_b8_s128_float16"))
+    text = generate_module(sched, Config(), inline_header=False).source
+    # the copy lives one directory below the device header
+    return text.replace('#include "mlcb_device.cuh"', '#include "../mlcb_device.cuh"')
+
+
+def write_example() -> pathlib.Path:
+    EXAMPLE.parent.mkdir(parents=True, exist_ok=True)
+    text = example_source()
+    if not EXAMPLE.exists() or EXAMPLE.read_text() != text:
+        EXAMPLE.write_text(text)
+    return EXAMPLE

@@ -154,3 +154,20 @@ def test_large_streaming_kernels_use_256_bit_accesses():
     assert small.launch["k0"].vector == 8
     off = generate_module(load_schedule("micro-gelu_b32_s128_float16"), Config(wide_access_bytes=0))
     assert off.launch["k0"].vector == 8
+
+
+def test_committed_example_translation_unit_is_current():
+    """csrc/examples holds the generated CUDA for BERT-base b8 verbatim."""
+    assert B.EXAMPLE.exists()
+    assert B.EXAMPLE.read_text() == B.example_source(), \
+        "regenerate with mlc_compiler_b200.build.write_example()"
+
+
+@needs_nvcc
+def test_example_compiles_against_the_device_header(tmp_path):
+    import subprocess
+
+    out = tmp_path / "example.cubin"
+    cmd = [B.nvcc_path(), *B.GENCODE, *B.NVCC_FLAGS, "-cubin", "-o", str(out), str(B.EXAMPLE)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
