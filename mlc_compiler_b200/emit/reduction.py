@@ -392,7 +392,8 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
 
         c.emit("#pragma unroll")
         c.emit(f"    for (int q = 0; q < {NP}; ++q) {{")
-        c.emit(f"        const int c0 = (lane + q * {G}) * {V};")
+        if geo.masked or first_loads or stores or gathers:
+            c.emit(f"        const int c0 = (lane + q * {G}) * {V};")
         ind = "        "
         if geo.masked:
             c.emit(f"        if (c0 < {k.n_cols}) {{")
