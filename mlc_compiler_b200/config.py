@@ -62,6 +62,9 @@ class Config:
     #: fold a pointwise producer into the pointwise kernels that only re-read it at
     #: another index (bias add + head-layout copy at batch > 1); bit-identical
     forward_into_copies: bool = True
+    #: turn ``mm`` + leading bias add into ``addmm`` (cuBLASLt bias epilogue).  Off by
+    #: default: it changes how the matmul is dispatched and rounds once instead of twice
+    bias_epilogue: bool = False
     #: streams the schedule is captured over.  1 reproduces the reference's single
     #: chain of graph nodes; more lets kernels with no dependency between them
     #: (physical byte ranges considered) run as parallel branches of the graph

@@ -136,8 +136,10 @@ class CompiledModel:
         # gathers) become parallel branches of the CUDA graph.  Generated and
         # library kernels are otherwise exactly the scheduled ones.
         work = schedule
+        if getattr(self.cfg, "bias_epilogue", False) and schedule.plan.mode == "arena":
+            work = rewrite.fold_bias_into_matmul(work)
         if getattr(self.cfg, "forward_into_copies", True) and schedule.plan.mode == "arena":
-            work = rewrite.forward_into_consumers(schedule)
+            work = rewrite.forward_into_consumers(work)
         self._exec = work
         self._streams = None
         n_streams = int(getattr(self.cfg, "graph_streams", 1) or 1)

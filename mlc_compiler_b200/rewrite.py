@@ -253,3 +253,193 @@ def _arena_clobbered(schedule, kernels, p, pi: int, last_reader: int) -> bool:
                 if sb is not None and b != a.buffer and sa[0] < sb[1] and sb[0] < sa[1]:
                     return True
     return False
+
+
+# --------------------------------------------------------------------------
+# bias epilogue (opt-in: it changes how a matmul is dispatched)
+# --------------------------------------------------------------------------
+
+def _col_only(m: kir.IndexMap, n_cols: int, var: str) -> bool:
+    """``m`` reads element ``column`` of a length-``n_cols`` vector."""
+    if m.base != 0:
+        return False
+    terms = [t for a in m.axes for t in a.terms]
+    if len(terms) != 1 or terms[0] != (n_cols, 1, 1):
+        return False
+    return all(a.var == var or not a.terms for a in m.axes)
+
+
+def _row_major(m: kir.IndexMap, rows: int, cols: int) -> bool:
+    """``m`` addresses a contiguous ``[rows, cols]`` matrix at ``(row, column)``."""
+    if m.base != 0:
+        return False
+    if len(m.axes) == 1:                                   # flat idx
+        return m.axes[0].terms == ((rows * cols, 1, 1),)
+    by = {a.var: a.terms for a in m.axes}
+    return by.get("row") == ((rows, 1, cols),) and by.get("col") == ((cols, 1, 1),)
+
+
+def _strip_bias_add(e, x_slot: int, b_slot: int):
+    """``e`` with the first ``add(Load(x), Load(b))`` (either order) replaced by
+    ``Load(x)``; returns ``(new expression, replaced?)``."""
+    if isinstance(e, Call):
+        if e.fn == "add" and len(e.args) == 2 and all(isinstance(a, Load) for a in e.args) \
+                and {e.args[0].slot, e.args[1].slot} == {x_slot, b_slot}:
+            return Load(x_slot), True
+        out, hit = [], False
+        for a in e.args:
+            if hit:
+                out.append(a)
+            else:
+                na, hit = _strip_bias_add(a, x_slot, b_slot)
+                out.append(na)
+        return Call(e.fn, tuple(out)), hit
+    if isinstance(e, Cast):
+        x, hit = _strip_bias_add(e.x, x_slot, b_slot)
+        return Cast(x, e.dtype), hit
+    return e, False
+
+
+def _drop_slot(k, slot: int):
+    """Kernel ``k`` without input ``slot`` (which nothing reads any more)."""
+    renum = {old: new for new, old in enumerate(i for i in range(len(k.inputs)) if i != slot)}
+
+    def fix(e):
+        if isinstance(e, Load):
+            return Load(renum[e.slot])
+        if isinstance(e, Call):
+            return Call(e.fn, tuple(fix(a) for a in e.args))
+        if isinstance(e, Cast):
+            return Cast(fix(e.x), e.dtype)
+        return e
+
+    inputs = [a for i, a in enumerate(k.inputs) if i != slot]
+    out_expr = {n: fix(e) for n, e in k.out_expr.items()}
+    if isinstance(k, kir.PointwiseKernel):
+        return kir.PointwiseKernel(k.name, k.space, inputs, list(k.outputs),
+                                   [(n, fix(e)) for n, e in k.body], out_expr, list(k.ops))
+    steps = [kir.Reduce(s.name, s.kind, fix(s.expr)) if isinstance(s, kir.Reduce)
+             else kir.Bind(s.name, fix(s.expr)) for s in k.steps]
+    return kir.ReductionKernel(k.name, k.row_space, k.reduce_space, inputs, list(k.outputs), steps,
+                               out_expr, set(k.row_outputs), k.two_pass, list(k.ops))
+
+
+def fold_bias_into_matmul(schedule: kir.Schedule) -> kir.Schedule:
+    """Turn ``mm`` followed by a generated kernel that starts with ``+ bias`` into
+    ``addmm`` (cuBLASLt bias epilogue) and remove the add from the kernel; a
+    kernel that was *only* the bias add disappears and the matmul writes its
+    output directly.
+
+    Not applied by default: the matmul is then no longer dispatched as the
+    reference dispatches it, and the bias is added to the fp32 accumulator
+    before the single rounding instead of after a first rounding to the buffer
+    dtype (a difference of at most one unit in the last place of fp16/bf16).
+    """
+    kernels = list(schedule.kernels)
+    outputs = {v.buffer for v in schedule.outputs}
+    i = 0
+    changed = False
+    while i < len(kernels):
+        e = kernels[i]
+        i += 1
+        if not (isinstance(e, kir.ExternKernel) and e.op == "aten.mm.default" and not e.kwargs
+                and len(e.args) == 2 and all(isinstance(a, kir.View) for a in e.args)
+                and len(e.outputs) == 1):
+            continue
+        x = e.outputs[0]
+        if x.buffer in outputs or len(x.shape) != 2 or x.offset != 0 \
+                or tuple(x.strides) != (x.shape[1], 1):
+            continue
+        rows, cols = x.shape
+        readers = [j for j, k in enumerate(kernels) if x.buffer in k.reads()]
+        if len(readers) != 1 or readers[0] < i:
+            continue
+        j = readers[0]
+        p = kernels[j]
+        if isinstance(p, kir.ExternKernel):
+            continue
+        var = "idx" if isinstance(p, kir.PointwiseKernel) else "col"
+        x_slots = [q for q, a in enumerate(p.inputs) if a.buffer == x.buffer]
+        if len(x_slots) != 1 or not _row_major(p.inputs[x_slots[0]].index, rows, cols):
+            continue
+        xs = x_slots[0]
+        done = False
+        for bs, b in enumerate(p.inputs):
+            spec = schedule.buffers[b.buffer]
+            if bs == xs or spec.kind != "param" or spec.numel != cols or b.dtype != p.inputs[xs].dtype \
+                    or not _col_only(b.index, cols, var):
+                continue
+            # the add must be the only use of both operands
+            exprs = ([ex for _, ex in p.body] if isinstance(p, kir.PointwiseKernel)
+                     else [s.expr for s in p.steps]) + list(p.out_expr.values())
+            uses_x = sum(1 for ex in exprs for sub in kir.walk(ex)
+                         if isinstance(sub, Load) and sub.slot == xs)
+            uses_b = sum(1 for ex in exprs for sub in kir.walk(ex)
+                         if isinstance(sub, Load) and sub.slot == bs)
+            if uses_x != 1 or uses_b != 1:
+                continue
+            hit = False
+
+            def strip(ex):
+                nonlocal hit
+                if hit:
+                    return ex
+                new, h = _strip_bias_add(ex, xs, bs)
+                hit = hit or h
+                return new
+
+            if isinstance(p, kir.PointwiseKernel):
+                body = [(n, strip(ex)) for n, ex in p.body]
+                out_expr = {n: strip(ex) for n, ex in p.out_expr.items()}
+                q = kir.PointwiseKernel(p.name, p.space, list(p.inputs), list(p.outputs), body,
+                                        out_expr, list(p.ops))
+            else:
+                steps = [kir.Reduce(s.name, s.kind, strip(s.expr)) if isinstance(s, kir.Reduce)
+                         else kir.Bind(s.name, strip(s.expr)) for s in p.steps]
+                out_expr = {n: strip(ex) for n, ex in p.out_expr.items()}
+                q = kir.ReductionKernel(p.name, p.row_space, p.reduce_space, list(p.inputs),
+                                        list(p.outputs), steps, out_expr, set(p.row_outputs),
+                                        p.two_pass, list(p.ops))
+            if not hit:
+                continue
+            q = _drop_slot(q, bs)
+            bias_view = kir.View(b.name, b.buffer, (cols,), (1,), 0)
+            target = x
+            # a kernel that was nothing but the bias add: let the matmul write its output
+            if isinstance(q, kir.PointwiseKernel) and len(q.outputs) == 1 and len(q.inputs) == 1:
+                o = q.outputs[0]
+                sole = q.out_expr[o.name]
+                while isinstance(sole, Ref):
+                    sole = dict(q.body).get(sole.name, sole)
+                    if isinstance(sole, Ref):
+                        break
+                plain = isinstance(sole, Load) or (isinstance(sole, Cast) and isinstance(sole.x, Load)
+                                                   and sole.dtype == o.dtype)
+                if plain and o.dtype == schedule.buffers[x.buffer].dtype \
+                        and _row_major(o.index, rows, cols) and o.buffer not in outputs:
+                    target = kir.View(o.name, o.buffer, (rows, cols), (cols, 1), 0)
+                    q = None
+            kernels[i - 1] = kir.ExternKernel(e.name, "aten.addmm.default",
+                                              [bias_view, e.args[0], e.args[1]], {}, [target])
+            if q is None:
+                del kernels[j]
+            else:
+                kernels[j] = q
+            changed = done = True
+            break
+        if not done:
+            continue
+    if not changed:
+        return schedule
+    from .concurrency import relax
+
+    out = kir.Schedule(name=schedule.name, kernels=kernels, buffers=schedule.buffers,
+                       inputs=schedule.inputs, outputs=schedule.outputs, params=schedule.params,
+                       plan=schedule.plan, meta=dict(schedule.meta))
+    if out.plan.mode == "arena":
+        live = out.live_buffers()
+        out.plan = kir.ArenaPlan(out.plan.mode, out.plan.arena_bytes,
+                                 {b: o for b, o in out.plan.offsets.items() if b in live},
+                                 out.plan.peak_bytes, out.plan.total_bytes)
+        out = relax(out)
+    return out

@@ -277,3 +277,26 @@ def test_every_kernel_of_a_model_matches_the_oracle_on_the_same_inputs(stem, dev
             assert_close(buffers[a.buffer], cpu[a.buffer], a.dtype, f"{stem} {k.name} ({k.summary()})")
         checked += 1
     assert checked == cm.generated_launches
+
+
+@pytest.mark.parametrize("name,batch", [("bert-base", 1), ("gpt2-small", 4)])
+def test_bias_epilogue_option_matches_the_oracle(name, batch, dev):
+    """Opt-in addmm epilogue with non-zero biases: same outputs as the schedule as
+    scheduled (oracle), within the fp16 bar."""
+    from mlc_compiler_b200.executor import CompiledModel
+
+    s = load_schedule(models.schedule_name(name, batch, torch.float16))
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    g = torch.Generator().manual_seed(11)
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, torch.nn.Linear) and m.bias is not None:
+                m.bias.copy_((torch.randn(m.bias.shape, generator=g) * 0.05).to(m.bias.dtype))
+    want, _ = oracle.run_schedule(s, model, inputs)
+    cm = CompiledModel(s, model, Config(bias_epilogue=True), dev)
+    ops = [k.op for k in cm.executed_schedule.kernels if isinstance(k, kir.ExternKernel)]
+    assert ops.count("aten.addmm.default") >= 48
+    cm(*[t.to(dev) for t in inputs])
+    got = cm(*[t.to(dev) for t in inputs])
+    torch.cuda.synchronize()
+    assert_close(got, want, "float16", f"{name} b{batch} with bias epilogue")

