@@ -221,3 +221,85 @@ class Gen:
         k = kir.ReductionKernel(name, (rows,), (cols,), inputs, outs, steps, out_expr, row_outputs,
                                 streamed, ["fuzz"])
         return k, specs, buffers
+
+
+def special_cases():
+    """Hand-shaped kernels for the code paths random small shapes cannot reach:
+    register-tile transposes, 256-bit accesses, narrow integer dtypes, fp64."""
+    g = torch.Generator().manual_seed(5)
+    kernels, specs, buffers = [], {}, {}
+
+    def buf(name, numel, dtype, kind="input", fill=None):
+        specs[name] = kir.BufferSpec(name, (numel,), dtype, kind)
+        if fill is None:
+            t = torch.zeros(numel, dtype=kir.torch_dtype(dtype))
+        elif dtype in kir.FLOAT_DTYPES:
+            t = (torch.randn(numel, generator=g) * 1.5).to(kir.torch_dtype(dtype))
+        elif dtype == "uint8":
+            t = torch.randint(0, 100, (numel,), generator=g).to(torch.uint8)
+        else:
+            t = torch.randint(-50, 50, (numel,), generator=g).to(kir.torch_dtype(dtype))
+        buffers[name] = t
+        return name
+
+    def flat(n):
+        return kir.IndexMap((kir.Axis("idx", n, ((n, 1, 1),)),))
+
+    # 1/2: transposes [B, R, T] <- storage [B, T, R], with a t-contiguous addend and a per-r bias
+    for tag, dt, (B, R, T) in (("tr16", "float16", (2, 128, 64)), ("trbf", "bfloat16", (3, 64, 96))):
+        n = B * R * T
+        x = buf(f"{tag}_x", n, dt, fill=1)
+        y = buf(f"{tag}_y", n, dt, fill=1)
+        b = buf(f"{tag}_b", R, dt, fill=1)
+        o = buf(f"{tag}_o", n, dt, "output")
+        ax = lambda terms: kir.IndexMap((kir.Axis("idx", n, terms),))
+        k = kir.PointwiseKernel(
+            tag, (B, R, T),
+            [kir.Operand(x, x, dt, ax(((B, R * T, R * T), (R, T, 1), (T, 1, R)))),
+             kir.Operand(y, y, dt, flat(n)),
+             kir.Operand(b, b, dt, ax(((R, T, 1),)))],
+            [kir.Operand(o, o, dt, flat(n))],
+            [("t0", kir.Call("add", (kir.Load(0), kir.Load(2)))),
+             ("t1", kir.Call("mul", (kir.Ref("t0"), kir.Call("tanh", (kir.Load(1),)))))],
+            {o: kir.Cast(kir.Ref("t1"), dt)}, ["transpose"])
+        kernels.append(k)
+
+    # 3: 24 MB streaming kernel -> 256-bit accesses
+    n = 1 << 22
+    x, y, o = buf("wide_x", n, "float16", fill=1), buf("wide_y", n, "float16", fill=1), \
+        buf("wide_o", n, "float16", "output")
+    kernels.append(kir.PointwiseKernel(
+        "wide", (n,), [kir.Operand(x, x, "float16", flat(n)), kir.Operand(y, y, "float16", flat(n))],
+        [kir.Operand(o, o, "float16", flat(n))],
+        [("t0", kir.Call("add", (kir.Load(0), kir.Call("mul", (kir.Load(1), kir.Const(2.0))))))],
+        {o: kir.Cast(kir.Ref("t0"), "float16")}, ["wide"]))
+
+    # 4: every narrow integer dtype in and out
+    n = 1000
+    for dt in ("int32", "int16", "int8", "uint8"):
+        x = buf(f"i_{dt}_x", n, dt, fill=1)
+        o = buf(f"i_{dt}_o", n, dt, "output")
+        f = buf(f"i_{dt}_f", n, "float32", "output")
+        kernels.append(kir.PointwiseKernel(
+            f"ints_{dt}", (n,), [kir.Operand(x, x, dt, flat(n))],
+            [kir.Operand(o, o, dt, flat(n)), kir.Operand(f, f, "float32", flat(n))],
+            [("t0", kir.Call("abs", (kir.Load(0),))),
+             ("t1", kir.Call("minimum", (kir.Ref("t0"), kir.Const(40)))),
+             ("t2", kir.Call("mul", (kir.Cast(kir.Ref("t1"), "float32"), kir.Const(0.5))))],
+            {o: kir.Cast(kir.Ref("t1"), dt), f: kir.Ref("t2")}, ["ints"]))
+
+    # 5: fp64 pointwise + row reduction
+    rows, cols = 7, 50
+    x = buf("d_x", rows * cols, "float64", fill=1)
+    o = buf("d_o", rows * cols, "float64", "output")
+    r = buf("d_r", rows, "float64", "output")
+    rc = kir.IndexMap((kir.Axis("row", rows, ((rows, 1, cols),)), kir.Axis("col", cols, ((cols, 1, 1),))))
+    kernels.append(kir.ReductionKernel(
+        "fp64", (rows,), (cols,), [kir.Operand(x, x, "float64", rc)],
+        [kir.Operand(o, o, "float64", rc),
+         kir.Operand(r, r, "float64", kir.IndexMap((kir.Axis("row", rows, ((rows, 1, 1),)),)))],
+        [kir.Bind("t0", kir.Call("exp", (kir.Call("mul", (kir.Load(0), kir.Const(0.25))),))),
+         kir.Reduce("r1", "sum", kir.Ref("t0")),
+         kir.Bind("t2", kir.Call("div", (kir.Ref("t0"), kir.Ref("r1"))))],
+        {o: kir.Ref("t2"), r: kir.Ref("r1")}, {r}, False, ["fp64"]))
+    return kir.Schedule("special", kernels, specs), buffers

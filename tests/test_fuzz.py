@@ -10,7 +10,7 @@ import torch
 
 import kir_oracle as oracle
 from conftest import assert_close
-from fuzz_kernels import Gen
+from fuzz_kernels import Gen, special_cases
 from mlc_compiler_b200 import Config, kir
 from mlc_compiler_b200 import build as B
 from mlc_compiler_b200.emit import generate_module
@@ -78,3 +78,31 @@ def test_corpus_matches_the_oracle_on_the_gpu(seed):
             except AssertionError as e:
                 failures.append(str(e))
     assert not failures, "\n".join(failures[:10])
+
+
+def test_special_cases_take_the_intended_code_paths():
+    sched, buffers = special_cases()
+    mod = generate_module(sched, Config())
+    assert "transposing" in mod.kernel_source("tr16") and "transposing" in mod.kernel_source("trbf")
+    assert mod.launch["wide"].vector == 16 and "mlcb_load<__half, 16>" in mod.kernel_source("wide")
+    assert "double" in mod.kernel_source("fp64")
+    for k in sched.kernels:
+        oracle.run_kernel(k, buffers)
+
+
+@pytest.mark.gpu
+def test_special_cases_match_the_oracle_on_the_gpu():
+    from mlc_compiler_b200.runtime import CudaRuntime
+
+    dev = torch.device("cuda", 0)
+    sched, buffers = special_cases()
+    rt = CudaRuntime(sched, Config(), dev)
+    for k in sched.kernels:
+        gpu = {b: buffers[b].to(dev) for b in set(k.reads()) | set(k.writes())}
+        for b in k.writes():
+            gpu[b].fill_(float("nan")) if gpu[b].is_floating_point() else gpu[b].fill_(1)
+        rt.launch(k, gpu)
+        oracle.run_kernel(k, buffers)
+        torch.cuda.synchronize()
+        for a in k.outputs:
+            assert_close(gpu[a.buffer], buffers[a.buffer], a.dtype, f"{k.name}/{a.name}")
