@@ -50,9 +50,9 @@ def main(argv=None) -> int:
 
     sched = load_schedule(args.schedule)
     if args.rewritten:
-        from .rewrite import forward_into_consumers
+        from .rewrite import prepare
 
-        sched = forward_into_consumers(sched)
+        sched = prepare(sched, Config())
     if args.command == "show":
         print(sched.format())
         return 0

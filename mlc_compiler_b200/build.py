@@ -126,9 +126,9 @@ def example_source() -> str:
     from .config import Config
     from .emit import generate_module
     from .frontend import load_schedule
-    from .rewrite import forward_into_consumers
+    from .rewrite import prepare
 
-    sched = forward_into_consumers(load_schedule("bert-base_b8_s128_float16"))
+    sched = prepare(load_schedule("bert-base_b8_s128_float16"), Config())
     text = generate_module(sched, Config(), inline_header=False).source
     # the copy lives one directory below the device header
     return text.replace('#include "mlcb_device.cuh"', '#include "../mlcb_device.cuh"')

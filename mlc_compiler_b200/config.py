@@ -62,6 +62,9 @@ class Config:
     #: fold a pointwise producer into the pointwise kernels that only re-read it at
     #: another index (bias add + head-layout copy at batch > 1); bit-identical
     forward_into_copies: bool = True
+    #: let a matmul store straight into the layout a following pure copy would have
+    #: produced (the context ``clone`` at batch 1); same op, same values, one launch fewer
+    write_through_copies: bool = True
     #: turn ``mm`` + leading bias add into ``addmm`` (cuBLASLt bias epilogue).  Off by
     #: default: it changes how the matmul is dispatched and rounds once instead of twice
     bias_epilogue: bool = False

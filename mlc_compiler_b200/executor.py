@@ -131,15 +131,12 @@ class CompiledModel:
 
         # What actually runs.  ``self.schedule`` stays what the frontend produced;
         # ``self._exec`` may (1) have pointwise producers folded into the copies
-        # that read them and (2) be re-ordered by data level with a re-packed
+        # that read them and copies folded into the matmul that feeds them, and
+        # (2) be re-ordered by data level with a re-packed
         # arena, so that independent neighbours (q/k/v projections, embedding
         # gathers) become parallel branches of the CUDA graph.  Generated and
         # library kernels are otherwise exactly the scheduled ones.
-        work = schedule
-        if getattr(self.cfg, "bias_epilogue", False) and schedule.plan.mode == "arena":
-            work = rewrite.fold_bias_into_matmul(work)
-        if getattr(self.cfg, "forward_into_copies", True) and schedule.plan.mode == "arena":
-            work = rewrite.forward_into_consumers(work)
+        work = rewrite.prepare(schedule, self.cfg)
         self._exec = work
         self._streams = None
         n_streams = int(getattr(self.cfg, "graph_streams", 1) or 1)

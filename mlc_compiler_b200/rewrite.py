@@ -27,6 +27,8 @@ for that producer.
 
 from __future__ import annotations
 
+import math
+
 from . import kir
 from .kir import Call, Cast, Load, Ref
 
@@ -218,16 +220,7 @@ def forward_into_consumers(schedule: kir.Schedule, max_body: int = 32,
     out = kir.Schedule(name=schedule.name, kernels=kernels, buffers=schedule.buffers,
                        inputs=schedule.inputs, outputs=schedule.outputs, params=schedule.params,
                        plan=schedule.plan, meta=dict(schedule.meta))
-    if replan:
-        from .concurrency import relax
-
-        live = out.live_buffers()
-        out.plan = kir.ArenaPlan(out.plan.mode, out.plan.arena_bytes,
-                                 {b: o for b, o in out.plan.offsets.items() if b in live},
-                                 out.plan.peak_bytes, out.plan.total_bytes,
-                                 out.plan.alloc_at, out.plan.free_at)
-        out = relax(out)
-    return out
+    return _replanned(out) if replan else out
 
 
 def _arena_clobbered(schedule, kernels, p, pi: int, last_reader: int) -> bool:
@@ -253,6 +246,134 @@ def _arena_clobbered(schedule, kernels, p, pi: int, last_reader: int) -> bool:
                 if sb is not None and b != a.buffer and sa[0] < sb[1] and sb[0] < sa[1]:
                     return True
     return False
+
+
+# --------------------------------------------------------------------------
+# copies after an extern: let the extern write the copy's layout itself
+# --------------------------------------------------------------------------
+
+#: externs whose ``out=`` may be any strided matrix (cuBLAS takes a leading
+#: dimension and a batch stride, so ATen hands such a destination straight on)
+_STRIDED_OUT = ("aten.mm.default", "aten.bmm.default", "aten.addmm.default")
+
+
+def _pure_copy(k) -> bool:
+    if not isinstance(k, kir.PointwiseKernel) or len(k.inputs) != 1 or len(k.outputs) != 1:
+        return False
+    e = k.out_expr[k.outputs[0].name]
+    while isinstance(e, Cast) and e.dtype in (k.inputs[0].dtype, "float32") \
+            and k.inputs[0].dtype in kir.FLOAT_DTYPES:
+        e = e.x                                  # widening and back is the identity
+    return (not k.body and isinstance(e, Load) and k.inputs[0].dtype == k.outputs[0].dtype
+            and k.inputs[0].buffer != k.outputs[0].buffer)
+
+
+def _destination_strides(view: kir.View, copy: kir.PointwiseKernel) -> tuple[int, ...] | None:
+    """Strides ``T`` such that element ``i`` of the extern's (dense) result lands
+    where the copy would have put it: ``dst[sum i_j T_j] = src[sum i_j S_j]``.
+    Exists when every dimension of the result is exactly one digit of the copy's
+    read map; a dimension the copy splits into two digits with unrelated
+    destination strides (heads and batch at batch > 1) has no single stride."""
+    src, dst = copy.inputs[0].index, copy.outputs[0].index
+    n = view.numel
+    if (src.base or dst.base or len(src.axes) != 1 or len(dst.axes) != 1 or copy.numel != n
+            or dst.axes[0].terms != ((n, 1, 1),) or view.offset != 0):
+        return None
+    digits = {s: (size, o) for size, o, s in src.axes[0].terms}
+    if len(digits) != len(src.axes[0].terms) or math.prod(z for z, _ in digits.values()) != n:
+        return None
+    strides = []
+    used = 0
+    for size, s in zip(view.shape, view.strides):
+        if size == 1:
+            strides.append(s)
+            continue
+        if digits.get(s, (0, 0))[0] != size:
+            return None
+        strides.append(digits[s][1])
+        used += 1
+    return tuple(strides) if used == len(digits) else None
+
+
+def write_through_copies(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
+    """Drop a pure copy that only re-lays an extern's result, by handing the
+    extern the copy's layout as its strided ``out=``.
+
+    At batch 1 the context matmul produces ``[H, T, D/H]`` and a ``clone``
+    permutes it to ``[T, H, D/H]`` for the output projection: one launch per
+    layer that moves no information.  ``bmm`` writes any matrix layout with a
+    leading dimension and a batch stride, so it can store ``[H, T, D/H]`` with
+    strides ``(D/H, D, 1)`` directly into the clone's buffer.  Values are
+    unchanged (a copy is exact); the op and its inputs are unchanged.  At
+    batch > 1 the clone splits the batched-heads dimension in two and no
+    strided view expresses it, so the copy stays."""
+    kernels = list(schedule.kernels)
+    finals = {v.buffer for v in schedule.outputs}
+    dropped = False
+    for ei in range(len(kernels)):
+        e = kernels[ei]
+        if not isinstance(e, kir.ExternKernel) or e.op not in _STRIDED_OUT or len(e.outputs) != 1:
+            continue
+        x = e.outputs[0]
+        spec = schedule.buffers[x.buffer]
+        if x.buffer in finals or not spec.plannable or x.numel != spec.numel:
+            continue
+        if any(s != d for s, d in zip(x.strides, _dense_strides(x.shape))):
+            continue
+        touching = [ci for ci, c in enumerate(kernels)
+                    if ci != ei and c is not None and (x.buffer in c.reads() or x.buffer in c.writes())]
+        if len(touching) != 1 or touching[0] < ei or not _pure_copy(kernels[touching[0]]):
+            continue
+        ci = touching[0]
+        c = kernels[ci]
+        y = c.outputs[0]
+        strides = _destination_strides(x, c)
+        if strides is None or x.buffer in e.reads() or y.buffer in e.reads():
+            continue
+        # the destination must not be touched between the extern and the copy
+        if any(k is not None and (y.buffer in k.reads() or y.buffer in k.writes())
+               for k in kernels[ei + 1:ci]):
+            continue
+        # ATen wants a matrix it can give cuBLAS: unit stride on one of the last two
+        # dimensions, the other at least as long as the row it steps over
+        if not _blas_layout(x.shape, strides):
+            continue
+        kernels[ei] = kir.ExternKernel(e.name, e.op, e.args, e.kwargs,
+                                       [kir.View(y.name, y.buffer, x.shape, strides, 0)])
+        kernels[ci] = None
+        dropped = True
+    if not dropped:
+        return schedule
+    out = kir.Schedule(name=schedule.name, kernels=[k for k in kernels if k is not None],
+                       buffers=schedule.buffers, inputs=schedule.inputs, outputs=schedule.outputs,
+                       params=schedule.params, plan=schedule.plan, meta=dict(schedule.meta))
+    return _replanned(out) if replan else out
+
+
+def _dense_strides(shape) -> tuple[int, ...]:
+    out, run = [], 1
+    for n in reversed(shape):
+        out.append(run)
+        run *= n
+    return tuple(reversed(out))
+
+
+def _blas_layout(shape, strides) -> bool:
+    if len(shape) < 2:
+        return False
+    (m, n), (sm, sn) = shape[-2:], strides[-2:]
+    return (sn == 1 and sm >= max(1, n)) or (sm == 1 and sn >= max(1, m))
+
+
+def _replanned(out: kir.Schedule) -> kir.Schedule:
+    from .concurrency import relax
+
+    live = out.live_buffers()
+    out.plan = kir.ArenaPlan(out.plan.mode, out.plan.arena_bytes,
+                             {b: o for b, o in out.plan.offsets.items() if b in live},
+                             out.plan.peak_bytes, out.plan.total_bytes,
+                             out.plan.alloc_at, out.plan.free_at)
+    return relax(out)
 
 
 # --------------------------------------------------------------------------
@@ -443,3 +564,19 @@ def fold_bias_into_matmul(schedule: kir.Schedule) -> kir.Schedule:
                                  out.plan.peak_bytes, out.plan.total_bytes)
         out = relax(out)
     return out
+
+
+def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
+    """Every rewrite ``cfg`` enables, in the order the executor applies them.
+    Only arena-planned schedules are rewritten: the rewrites change live ranges
+    and re-pack the arena afterwards."""
+    if schedule.plan.mode != "arena":
+        return schedule
+    work = schedule
+    if getattr(cfg, "bias_epilogue", False):
+        work = fold_bias_into_matmul(work)
+    if getattr(cfg, "forward_into_copies", True):
+        work = forward_into_consumers(work)
+    if getattr(cfg, "write_through_copies", True):
+        work = write_through_copies(work)
+    return work

@@ -279,7 +279,7 @@ def run_extern(k: kir.ExternKernel, buffers: dict[str, torch.Tensor]) -> None:
 
     got = target(*[tensor(a) for a in k.args], **{n: tensor(a) for n, a in k.kwargs.items()})
     for view, t in zip(k.outputs, got if isinstance(got, (list, tuple)) else [got]):
-        buffers[view.buffer].copy_(t.contiguous().reshape(-1))
+        view.as_torch(buffers[view.buffer]).copy_(t)
 
 
 def run_kernel(k, buffers: dict[str, torch.Tensor]) -> None:

@@ -114,3 +114,69 @@ def test_bias_epilogue_leaves_other_matmuls_alone():
     d = load_tiny("attention__default__float32")
     out, _ = oracle.run_schedule(r, d["params"], d["inputs"])
     torch.testing.assert_close(out, d["outputs"][0], rtol=1e-5, atol=1e-6)
+
+
+# ---- copies after an extern ---------------------------------------------------
+
+@pytest.mark.parametrize("name,dtype", [("bert-base", torch.float16), ("gpt2-small", torch.float16),
+                                        ("bert-base", torch.float32)])
+def test_write_through_drops_the_context_clone_at_batch_one(name, dtype):
+    s = load_schedule(models.schedule_name(name, 1, dtype))
+    r = rewrite.write_through_copies(s)
+    assert len(s) - len(r) == 12 and r.counts()["extern"] == s.counts()["extern"]
+    strided = [k for k in r.kernels if isinstance(k, kir.ExternKernel)
+               and k.outputs[0].strides == (64, 768, 1)]
+    assert len(strided) == 12 and all(k.op == "aten.bmm.default" for k in strided)
+    gone = {k.name for k in s.kernels} - {k.name for k in r.kernels}
+    assert all(next(k for k in s.kernels if k.name == g).ops == ["clone"] for g in gone)
+    model, inputs = models.build(name, 1, dtype=dtype)
+    a, _ = oracle.run_schedule(s, model, inputs)
+    b, _ = oracle.run_schedule(r, model, inputs)
+    assert torch.equal(a, b)
+    assert r.plan.arena_bytes <= s.plan.arena_bytes
+
+
+def test_write_through_leaves_split_dimensions_alone():
+    # at batch 4 the clone splits [B*H] into (B, H) with unrelated destination
+    # strides: no strided matrix expresses it
+    s = rewrite.forward_into_consumers(load_schedule(models.schedule_name("bert-base", 4, torch.float16)))
+    assert rewrite.write_through_copies(s) is s
+
+
+def test_destination_strides_by_brute_force():
+    H, T, D = 3, 5, 4
+    n = H * T * D
+    view = kir.View("x", "x", (H, T, D), (T * D, D, 1))
+    copy = kir.PointwiseKernel(
+        "c", (1, T, H, D),
+        [kir.Operand("x", "x", "float32", _ax(n, (T, H * D, D), (H, D, T * D), (D, 1, 1)))],
+        [kir.Operand("y", "y", "float32", _ax(n, (n, 1, 1)))], [], {"y": kir.Load(0)}, ["clone"])
+    t = rewrite._destination_strides(view, copy)
+    assert t == (D, H * D, 1)
+    x = torch.arange(n, dtype=torch.float32)
+    want = torch.empty(n)
+    for i in range(n):
+        want[i] = x[copy.inputs[0].index.offset(idx=i)]
+    got = torch.empty(n)
+    got.as_strided((H, T, D), t).copy_(x.view(H, T, D))
+    assert torch.equal(got, want)
+    # a read map that repeats a digit, or does not cover the result, is refused
+    bad = kir.PointwiseKernel(
+        "c", (n,), [kir.Operand("x", "x", "float32", _ax(n, (T, H * D, D), (H * D, 1, 1)))],
+        copy.outputs, [], {"y": kir.Load(0)}, ["clone"])
+    assert rewrite._destination_strides(view, bad) is None
+
+
+def test_write_through_refuses_a_result_with_a_second_reader():
+    s = load_schedule(models.schedule_name("bert-base", 1, torch.float16))
+    clone = next(k for k in s.kernels if isinstance(k, kir.PointwiseKernel) and k.ops == ["clone"])
+    extra = kir.PointwiseKernel("spy", clone.space, list(clone.inputs),
+                                [kir.Operand("spy_out", "spy_out", "float16", clone.outputs[0].index)],
+                                [], {"spy_out": kir.Load(0)}, ["clone"])
+    buffers = dict(s.buffers)
+    buffers["spy_out"] = kir.BufferSpec("spy_out", (clone.numel,), "float16", "intermediate")
+    at = s.kernels.index(clone) + 1
+    t = kir.Schedule(s.name, s.kernels[:at] + [extra] + s.kernels[at:], buffers, s.inputs, s.outputs,
+                     s.params, s.plan, dict(s.meta))
+    r = rewrite.write_through_copies(t, replan=False)
+    assert len(t) - len(r) == 11 and clone.name in {k.name for k in r.kernels}
