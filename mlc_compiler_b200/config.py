@@ -65,6 +65,9 @@ class Config:
     #: let a matmul store straight into the layout a following pure copy would have
     #: produced (the context ``clone`` at batch 1); same op, same values, one launch fewer
     write_through_copies: bool = True
+    #: fetch embedding rows inside the row reduction that consumes them instead of
+    #: through a separate library gather (same table entries, bit-identical)
+    fold_embeddings: bool = True
     #: turn ``mm`` + leading bias add into ``addmm`` (cuBLASLt bias epilogue).  Off by
     #: default: it changes how the matmul is dispatched and rounds once instead of twice
     bias_epilogue: bool = False

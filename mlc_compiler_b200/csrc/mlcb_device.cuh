@@ -191,6 +191,12 @@ __device__ __forceinline__ void mlcb_store_at(T* __restrict__ p,
     mlcb_store<T, W>(p, tmp);
 }
 
+// Row id of a gathered operand, forced into the table: an id outside [0, n)
+// reads a wrong row instead of memory that is not the table's.
+__device__ __forceinline__ long long mlcb_clamp_index(long long v, long long n) {
+    return v < 0 ? 0 : (v >= n ? n - 1 : v);
+}
+
 template <typename T>
 __device__ __forceinline__ typename mlcb_elem<T>::reg mlcb_load1(const T* __restrict__ p) {
     return mlcb_elem<T>::get(*p);
@@ -257,7 +263,10 @@ __device__ __forceinline__ i64 mlcb_ipow(i64 b, i64 e) {
     while (e) { if (e & 1) r *= b; b *= b; e >>= 1; }
     return r;
 }
-template <typename T> __device__ __forceinline__ T mlcb_iabs(T x) { return x < 0 ? -x : x; }
+template <typename T> __device__ __forceinline__ T mlcb_iabs(T x) {
+    if constexpr (T(-1) > T(0)) return x;        // unsigned
+    else return x < 0 ? -x : x;
+}
 
 // ---------------------------------------------------------------------------
 // reductions

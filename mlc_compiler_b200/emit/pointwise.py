@@ -79,6 +79,8 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
     name = name or k.name
     numel = k.numel
     operands = list(k.inputs) + list(k.outputs)
+    if any(a.via is not None for a in operands):
+        raise ValueError(f"{k.name}: row gathers are only emitted for reduction inputs")
     if buffers is not None:
         for a in operands:
             check_bounds(a.index, buffers[a.buffer].numel, f"{k.name}:{a.name}")

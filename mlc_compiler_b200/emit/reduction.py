@@ -239,7 +239,17 @@ def _row_offsets(c: _Ctx, operands, prefix: str) -> None:
     for i, a in enumerate(operands):
         if prefix == "in" and not a.index.varies_along("col"):
             continue
-        off = render_offset(a.index, {"row": "row"}, skip=("col",))
+        if prefix == "out" and a.name in c.k.row_outputs:
+            continue                               # stored once per row, at its own offset
+        row = "row"
+        if prefix == "in" and a.via is not None:
+            # row gather: the table row is the integer operand `slot` holds for this
+            # row, clamped so that a bad id reads a wrong row, never out of bounds
+            slot, table_rows = a.via
+            row = f"in{i}_id"
+            c.emit(f"    const {c.it} {row} = ({c.it})mlcb_clamp_index((long long)s{slot}, "
+                   f"{table_rows});  // {a.name}[{c.k.inputs[slot].name}]")
+        off = render_offset(a.index, {"row": row}, skip=("col",))
         c.emit(f"    const {c.it} {prefix}{i}_r = {off};")
 
 
@@ -270,7 +280,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
     _row_setup(c, k.n_rows, len(reduces))
     scalar_in = _scalar_loads(c)
     _row_offsets(c, k.inputs, "in")
-    _row_offsets(c, [a if a.name not in k.row_outputs else a for a in k.outputs], "out")
+    _row_offsets(c, k.outputs, "out")
 
     # ---- which phase defines / uses each column-varying value -------------
     phase_of: dict[str, int] = {}
@@ -797,6 +807,17 @@ def emit_reduction(k: kir.ReductionKernel, cfg, buffers: dict[str, kir.BufferSpe
     if buffers is not None:
         for a in list(k.inputs) + list(k.outputs):
             check_bounds(a.index, buffers[a.buffer].numel, f"{k.name}:{a.name}")
+    for i, a in enumerate(k.inputs):
+        if a.via is None:
+            continue
+        slot, table_rows = a.via
+        ids = k.inputs[slot]
+        ax = a.index.axis("row")
+        if (ids.index.varies_along("col") or ids.dtype not in ("int64", "int32")
+                or ax is None or ax.numel != table_rows or not a.index.varies_along("col")):
+            raise ValueError(f"{k.name}:{a.name}: malformed row gather")
+    if any(a.via is not None for a in k.outputs):
+        raise ValueError(f"{k.name}: outputs cannot be gathered")
     name = name or k.name
     with X.math_mode(X.wants_fast_math(k, cfg)):
         return _emit_streamed(k, cfg, name) if k.two_pass else _emit_persistent(k, cfg, name)

@@ -243,6 +243,12 @@ class Operand:
     buffer: str
     dtype: str
     index: IndexMap
+    #: row gather (reduction inputs only; the reference has no such operand, its
+    #: embeddings are separate library calls): ``(slot, rows)`` means the ``row``
+    #: variable of ``index`` is not the kernel's row but the integer that input
+    #: ``slot`` -- an operand indexed by row alone -- holds for this row, clamped
+    #: to ``[0, rows)``; ``index``'s row axis then spans the table's ``rows``
+    via: tuple[int, int] | None = None
 
 
 # --------------------------------------------------------------------------
@@ -614,11 +620,12 @@ def _dec_index(j) -> IndexMap:
 
 
 def _enc_operand(a: Operand):
-    return [a.name, a.buffer, a.dtype, _enc_index(a.index)]
+    j = [a.name, a.buffer, a.dtype, _enc_index(a.index)]
+    return j + [list(a.via)] if a.via is not None else j
 
 
 def _dec_operand(j) -> Operand:
-    return Operand(j[0], j[1], j[2], _dec_index(j[3]))
+    return Operand(j[0], j[1], j[2], _dec_index(j[3]), tuple(j[4]) if len(j) > 4 else None)
 
 
 def _enc_view(v: View):

@@ -566,6 +566,161 @@ def fold_bias_into_matmul(schedule: kir.Schedule) -> kir.Schedule:
     return out
 
 
+# --------------------------------------------------------------------------
+# embeddings: gather the table row inside the kernel that consumes it
+# --------------------------------------------------------------------------
+
+def _constant_fill(k) -> int | None:
+    """The integer a kernel fills its single output with, if that is all it does."""
+    if (isinstance(k, kir.PointwiseKernel) and not k.inputs and _identity_output(k)):
+        e = k.out_expr[k.outputs[0].name]
+        while isinstance(e, Cast):
+            e = e.x
+        if isinstance(e, kir.Const) and isinstance(e.value, int) and not isinstance(e.value, bool):
+            return int(e.value)
+    return None
+
+
+def _token_map(a: kir.Operand, width: int, rows: int):
+    """For an operand that reads ``[tokens, width]`` rows whole (``col`` walks one
+    row, ``row`` picks the token): the map ``row -> token`` as a one-axis map."""
+    col, row = a.index.axis("col"), a.index.axis("row")
+    if (a.index.base or len(a.index.axes) != 2 or col is None or row is None
+            or col.terms != ((width, 1, 1),)):
+        return None
+    terms = []
+    for size, o, s in row.terms:
+        if s % width:
+            return None
+        terms.append((size, o, s // width))
+    return kir.IndexMap((kir.Axis("row", rows, tuple(terms)),))
+
+
+def fold_embeddings(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
+    """Drop ``aten.embedding`` calls whose result only feeds row reductions, by
+    letting the reduction fetch the table row itself.
+
+    BERT's embedding LayerNorm reads three ``[tokens, D]`` arrays that three
+    library gathers have just written (word, position and token-type rows; the
+    token-type ids come from a ``full_like(0)`` kernel); GPT-2's first LayerNorm
+    reads two.  A row reduction already loads each row as ``base + row_offset +
+    col``: taking ``row_offset`` from ``table_row[ids[row]]`` instead of from the
+    row number costs one 8-byte load per row and removes the gather, its launch
+    and the round trip of ``tokens x D`` elements through memory.  Ids that a
+    kernel fills with a constant become a plain broadcast row of the table and
+    the fill disappears as well.  The values read are the same table entries, so
+    results are bit-identical; an id outside the table reads a clamped row where
+    the library call would have raised a device assertion."""
+    kernels: list = list(schedule.kernels)
+    finals = {v.buffer for v in schedule.outputs}
+    changed = False
+    for ei, e in enumerate(kernels):
+        if not isinstance(e, kir.ExternKernel) or e.op != "aten.embedding.default":
+            continue
+        if len(e.args) < 2 or len(e.outputs) != 1:
+            continue
+        table, ids, x = e.args[0], e.args[1], e.outputs[0]
+        if not (isinstance(table, kir.View) and isinstance(ids, kir.View)):
+            continue
+        if len(table.shape) != 2 or table.strides != (table.shape[1], 1) or table.shape[1] < 2:
+            continue
+        n_table, width = table.shape
+        spec = schedule.buffers[x.buffer]
+        if (x.buffer in finals or not spec.plannable or x.offset or x.numel != spec.numel
+                or x.strides != _dense_strides(x.shape) or x.numel != ids.numel * width):
+            continue
+        if schedule.buffers[ids.buffer].dtype not in ("int64", "int32"):
+            continue
+        users = [ci for ci, c in enumerate(kernels) if c is not None and ci != ei
+                 and (x.buffer in c.reads() or x.buffer in c.writes())]
+        if not users or min(users) < ei or not all(
+                isinstance(kernels[ci], kir.ReductionKernel) and x.buffer not in kernels[ci].writes()
+                for ci in users):
+            continue
+        # ids and table must still hold the same data when the last consumer runs
+        if any(c is not None and (ids.buffer in c.writes() or table.buffer in c.writes())
+               for c in kernels[ei + 1:max(users) + 1]):
+            continue
+        fill = None
+        writers = [c for c in kernels[:ei] if c is not None and ids.buffer in c.writes()]
+        if len(writers) == 1:
+            fill = _constant_fill(writers[0])
+            if fill is not None and writers[0].numel != schedule.buffers[ids.buffer].numel:
+                fill = None
+        # token t of the ids view -> element of the ids buffer
+        dims: list[list[int]] = []                 # innermost first, dense neighbours merged
+        for size, stride in zip(reversed(ids.shape), reversed(ids.strides)):
+            if size == 1:
+                continue
+            if dims and stride == dims[-1][0] * dims[-1][1]:
+                dims[-1][0] *= size
+            else:
+                dims.append([size, stride])
+        run, inner_terms = 1, []
+        for size, stride in dims:
+            inner_terms.append((size, run, stride))
+            run *= size
+        ids_map = kir.IndexMap((kir.Axis("idx", ids.numel, tuple(reversed(inner_terms))),), ids.offset)
+
+        new: dict[int, kir.ReductionKernel] = {}
+        try:
+            for ci in users:
+                c = kernels[ci]
+                inputs = list(c.inputs)
+                if c.n_cols != width:
+                    raise _NoCompose
+                for slot, a in enumerate(c.inputs):
+                    if a.buffer != x.buffer:
+                        continue
+                    tok = _token_map(a, width, c.n_rows)
+                    if tok is None or a.dtype != schedule.buffers[table.buffer].dtype:
+                        raise _NoCompose
+                    if fill is not None:
+                        at = min(max(fill, 0), n_table - 1)
+                        inputs[slot] = kir.Operand(table.name, table.buffer, a.dtype, kir.IndexMap(
+                            (kir.Axis("row", c.n_rows, ()), kir.Axis("col", width, ((width, 1, 1),))),
+                            table.offset + at * width))
+                        continue
+                    where = compose(tok, ids_map, ids.numel)
+                    id_operand = kir.Operand(ids.name, ids.buffer, schedule.buffers[ids.buffer].dtype,
+                                             kir.IndexMap((where.axes[0], kir.Axis("col", width, ())),
+                                                          where.base))
+                    for q, have in enumerate(inputs):
+                        if (have.buffer, have.dtype, have.index, have.via) == \
+                                (id_operand.buffer, id_operand.dtype, id_operand.index, None):
+                            id_slot = q
+                            break
+                    else:
+                        inputs.append(id_operand)
+                        id_slot = len(inputs) - 1
+                    inputs[slot] = kir.Operand(table.name, table.buffer, a.dtype, kir.IndexMap(
+                        (kir.Axis("row", n_table, ((n_table, 1, width),)),
+                         kir.Axis("col", width, ((width, 1, 1),))), table.offset), (id_slot, n_table))
+                new[ci] = kir.ReductionKernel(c.name, c.row_space, c.reduce_space, inputs,
+                                              list(c.outputs), list(c.steps), dict(c.out_expr),
+                                              set(c.row_outputs), c.two_pass,
+                                              ["embedding"] + list(c.ops))
+        except _NoCompose:
+            continue
+        for ci, c in new.items():
+            kernels[ci] = c
+        kernels[ei] = None
+        changed = True
+    if not changed:
+        return schedule
+    # fills nobody reads any more
+    for pi, p in enumerate(kernels):
+        if p is not None and _constant_fill(p) is not None:
+            b = p.outputs[0].buffer
+            if b not in finals and not any(c is not None and c is not p and b in c.reads()
+                                           for c in kernels):
+                kernels[pi] = None
+    out = kir.Schedule(name=schedule.name, kernels=[k for k in kernels if k is not None],
+                       buffers=schedule.buffers, inputs=schedule.inputs, outputs=schedule.outputs,
+                       params=schedule.params, plan=schedule.plan, meta=dict(schedule.meta))
+    return _replanned(out) if replan else out
+
+
 def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
     """Every rewrite ``cfg`` enables, in the order the executor applies them.
     Only arena-planned schedules are rewritten: the rewrites change live ranges
@@ -579,4 +734,6 @@ def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
         work = forward_into_consumers(work)
     if getattr(cfg, "write_through_copies", True):
         work = write_through_copies(work)
+    if getattr(cfg, "fold_embeddings", True):
+        work = fold_embeddings(work)
     return work

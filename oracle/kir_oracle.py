@@ -172,7 +172,16 @@ class _Span:
         if slot not in self._operands:
             r = self.rows
             a = r.k.inputs[slot]
-            off = offsets(a.index, row=r.row, col=self.col)
+            row = r.row
+            if a.via is not None:
+                # row gather: the row of the table is the integer another operand
+                # holds for this row (``aten.embedding`` folded into its consumer)
+                slot, table_rows = a.via
+                ids = r.k.inputs[slot]
+                at = offsets(ids.index, row=r.row, col=torch.zeros((1, 1), dtype=torch.int64))
+                row = r.buffers[ids.buffer][at.expand(r.k.n_rows, 1)].to(torch.int64)
+                row = row.clamp(0, table_rows - 1)
+            off = offsets(a.index, row=row, col=self.col)
             self._operands[slot] = widen(r.buffers[a.buffer][off.expand(r.k.n_rows, self.width)])
         return self._operands[slot]
 

@@ -302,4 +302,33 @@ def special_cases():
          kir.Reduce("r1", "sum", kir.Ref("t0")),
          kir.Bind("t2", kir.Call("div", (kir.Ref("t0"), kir.Ref("r1"))))],
         {o: kir.Ref("t2"), r: kir.Ref("r1")}, {r}, False, ["fp64"]))
+    # 6: rows gathered from a table by id (ids strided, out of range at both ends,
+    #    table at an offset), persistent and streamed, three dtypes
+    for tag, dt, idt, two_pass, (rows, width, table_rows) in (
+            ("gath16", "float16", "int64", False, (37, 96, 11)),
+            ("gathbf", "bfloat16", "int32", False, (64, 256, 5)),
+            ("gath32", "float32", "int64", True, (9, 2500, 7))):
+        skip = 2 * width                                      # table starts two rows into its buffer
+        tab = buf(f"{tag}_t", skip + table_rows * width, dt, fill=1)
+        ids = buf(f"{tag}_i", 2 * rows, idt, fill=1)          # values in [-50, 50): some outside the table
+        y = buf(f"{tag}_y", rows * width, dt, fill=1)
+        o = buf(f"{tag}_o", rows * width, dt, "output")
+        r = buf(f"{tag}_r", rows, "float32", "output")
+        rc = kir.IndexMap((kir.Axis("row", rows, ((rows, 1, width),)),
+                           kir.Axis("col", width, ((width, 1, 1),))))
+        kernels.append(kir.ReductionKernel(
+            tag, (rows,), (width,),
+            [kir.Operand(tab, tab, dt, kir.IndexMap(
+                (kir.Axis("row", table_rows, ((table_rows, 1, width),)),
+                 kir.Axis("col", width, ((width, 1, 1),))), skip), (2, table_rows)),
+             kir.Operand(y, y, dt, rc),
+             kir.Operand(ids, ids, idt, kir.IndexMap(
+                 (kir.Axis("row", rows, ((rows, 1, 2),)), kir.Axis("col", width, ())), 1))],
+            [kir.Operand(o, o, dt, rc),
+             kir.Operand(r, r, "float32", kir.IndexMap((kir.Axis("row", rows, ((rows, 1, 1),)),)))],
+            [kir.Bind("t0", kir.Call("add", (kir.Load(0), kir.Call("mul", (kir.Load(1), kir.Const(0.5)))))),
+             kir.Reduce("r1", "max", kir.Ref("t0")),
+             kir.Bind("t2", kir.Call("sub", (kir.Ref("t0"), kir.Ref("r1")))),
+             kir.Bind("t3", kir.Cast(kir.Ref("t2"), dt))],
+            {o: kir.Ref("t3"), r: kir.Ref("r1")}, {r}, two_pass, ["embedding"]))
     return kir.Schedule("special", kernels, specs), buffers

@@ -221,3 +221,24 @@ def test_matmul_writing_the_clone_layout_changes_nothing_but_the_launch_count(na
     # same op on the same operands; only the destination's leading dimension differs,
     # which may change cuBLAS's choice of kernel but not what is computed
     assert (a - b).abs().max().item() <= 1e-2 * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,batch", [("bert-base", 1), ("gpt2-small", 1), ("bert-base", 8)])
+def test_embeddings_gathered_by_the_layernorm_are_bit_identical(name, batch):
+    import torch
+    from mlc_compiler_b200 import Config, models
+    from mlc_compiler_b200.executor import CompiledModel
+    from mlc_compiler_b200.frontend import load_schedule
+
+    dev = torch.device("cuda", 0)
+    s = load_schedule(models.schedule_name(name, batch, torch.float16))
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    on = CompiledModel(s, model, Config(), dev)
+    off = CompiledModel(s, model, Config(fold_embeddings=False), dev)
+    assert len(off.executed_schedule) - len(on.executed_schedule) == (4 if name == "bert-base" else 2)
+    g = torch.Generator().manual_seed(11)
+    for _ in range(3):
+        ids = torch.randint(0, 30522, inputs[0].shape, generator=g)
+        di = [ids.to(dev)] + [t.to(dev) for t in inputs[1:]]
+        assert torch.equal(on(*di), off(*di))

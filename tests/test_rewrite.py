@@ -7,7 +7,7 @@ import torch
 
 import kir_oracle as oracle
 from conftest import load_tiny, tiny_cases
-from mlc_compiler_b200 import kir, models, rewrite
+from mlc_compiler_b200 import Config, kir, models, rewrite
 from mlc_compiler_b200.frontend import load_schedule
 
 
@@ -180,3 +180,64 @@ def test_write_through_refuses_a_result_with_a_second_reader():
                      s.params, s.plan, dict(s.meta))
     r = rewrite.write_through_copies(t, replan=False)
     assert len(t) - len(r) == 11 and clone.name in {k.name for k in r.kernels}
+
+
+# ---- embeddings gathered by their consumer --------------------------------------
+
+@pytest.mark.parametrize("stem,removed", [("bert-base_b1_s128_float16", 4), ("bert-base_b4_s128_float16", 4),
+                                          ("gpt2-small_b1_s128_float16", 2),
+                                          ("bert-base-streamed_b1_s128_float16", 4)])
+def test_embeddings_move_into_the_first_layernorm(stem, removed):
+    s = load_schedule(stem)
+    r = rewrite.fold_embeddings(s)
+    assert len(s) - len(r) == removed
+    assert not any(isinstance(k, kir.ExternKernel) and "embedding" in k.op for k in r.kernels)
+    assert not any(isinstance(k, kir.PointwiseKernel) and k.ops == ["full_like"] for k in r.kernels)
+    first = next(k for k in r.kernels if isinstance(k, kir.ReductionKernel))
+    gathered = [a for a in first.inputs if a.via is not None]
+    assert len(gathered) == 2                       # word and position rows; token type is a constant row
+    for a in gathered:
+        ids = first.inputs[a.via[0]]
+        assert ids.dtype == "int64" and not ids.index.varies_along("col")
+        assert a.index.axis("row").numel == a.via[1] == s.buffers[a.buffer].numel // 768
+    name, batch = stem.split("_")[0].replace("-streamed", ""), int(stem.split("_b")[1].split("_")[0])
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    a, _ = oracle.run_schedule(s, model, inputs)
+    b, _ = oracle.run_schedule(r, model, inputs)
+    assert torch.equal(a, b)
+    back = kir.loads(kir.dumps(r))
+    assert [x.via for k in back.generated() for x in k.inputs] == \
+        [x.via for k in r.generated() for x in k.inputs]
+
+
+def test_gathered_rows_are_clamped_into_the_table():
+    s = load_schedule("gpt2-small_b1_s128_float16")
+    r = rewrite.fold_embeddings(s)
+    first = next(k for k in r.kernels if isinstance(k, kir.ReductionKernel))
+    model, inputs = models.build("gpt2-small", 1, dtype=torch.float16)
+    good = oracle.allocate(r, model, inputs)
+    bad = oracle.allocate(r, model, [torch.full_like(inputs[0], 10 ** 9)])
+    last = oracle.allocate(r, model, [torch.full_like(inputs[0], 50256)])
+    oracle.run_kernel(first, good)
+    oracle.run_kernel(first, bad)
+    oracle.run_kernel(first, last)
+    out = first.outputs[0].buffer
+    assert torch.equal(bad[out], last[out]) and not torch.equal(bad[out], good[out])
+    from mlc_compiler_b200.emit import generate_module
+    assert "mlcb_clamp_index((long long)s4, 50257)" in generate_module(r, Config()).kernel_source(first.name)
+
+
+def test_embedding_with_other_readers_stays_a_library_call():
+    s = load_schedule("gpt2-small_b1_s128_float16")
+    emb = next(k for k in s.kernels if isinstance(k, kir.ExternKernel) and "embedding" in k.op)
+    x = emb.outputs[0]
+    n = x.numel
+    spy = kir.PointwiseKernel("spy", (n,), [kir.Operand(x.name, x.buffer, "float16", _ax(n, (n, 1, 1)))],
+                              [kir.Operand("spy_out", "spy_out", "float16", _ax(n, (n, 1, 1)))],
+                              [], {"spy_out": kir.Load(0)}, ["clone"])
+    buffers = dict(s.buffers)
+    buffers["spy_out"] = kir.BufferSpec("spy_out", (n,), "float16", "intermediate")
+    t = kir.Schedule(s.name, s.kernels[:2] + [spy] + s.kernels[2:], buffers, s.inputs, s.outputs,
+                     s.params, s.plan, dict(s.meta))
+    r = rewrite.fold_embeddings(t, replan=False)
+    assert emb.name in {k.name for k in r.kernels} and len(t) - len(r) == 1
