@@ -7,12 +7,10 @@ One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line
 * ``value`` / ``ms_per_step``: latency of one graph replay with the inputs already
   in device memory, per-step CUDA events, L2 flushed (a 256 MiB write) between
   steps, mean over exactly K steps, max over ranks.
-* ``e2e``: the same forward through the public host-buffer call
-  ``compiled.run_host(*host_inputs)``: host inputs in, host result out, the
-  copies in both directions inside the timed region (they are nodes of the same
-  graph launch as the kernels), host wall clock around each call, which returns
-  synchronised.  ``separate_copies_ms`` is the same through ``compiled(*pinned)``
-  followed by a copy back, every copy a stream operation of its own.
+* ``e2e``: the same forward through the public call ``compiled(*host_inputs)``:
+  pinned host inputs are copied in, the graph replayed, the result copied back
+  to pinned host memory, host wall clock around each step (device drained at the
+  end of every step).
 * ``roofline``: the largest fused-kernel microbenchmark (bias+GELU+residual over
   [32*128, 3072] fp16), timed live as a CUDA graph of launches over rotating
   buffer sets totalling more than four times L2; ``fused_kernels`` lists all nine
@@ -160,31 +158,21 @@ def time_replays(cm, dev_inputs, steps: int, warmup: int, flush) -> list[float]:
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
 
-def time_end_to_end(cm, host_inputs, steps: int, warmup: int, flush, single_graph: bool = True
-                    ) -> tuple[list[float], int, int]:
-    """Host wall clock of one forward from host buffers to host result, per step.
-
-    ``single_graph``: through ``CompiledModel.run_host`` (copy-in, kernels and
-    copy-out are nodes of one graph launch).  Otherwise through
-    ``compiled(*pinned)`` plus a copy back: every copy its own stream operation."""
+def time_end_to_end(cm, host_inputs, steps: int, warmup: int, flush) -> tuple[list[float], int, int]:
+    """Host wall clock of copy-in, replay, copy-out, per step."""
     pinned = [t.contiguous().pin_memory() for t in host_inputs]
     out = cm(*pinned)
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in pinned)
     d2h = host_out.numel() * host_out.element_size()
-    if single_graph:
-        cm.run_host(*host_inputs)
     times = []
     for i in range(warmup + steps):
         flush()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        if single_graph:
-            cm.run_host(*host_inputs)
-        else:
-            out = cm(*pinned)
-            host_out.copy_(out, non_blocking=True)
-            torch.cuda.synchronize()
+        out = cm(*pinned)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
         t1 = time.perf_counter()
         if i >= warmup:
             times.append((t1 - t0) * 1e3)
@@ -451,8 +439,6 @@ def run_ours(args) -> int:
         return 0
     e2e_times, h2d, d2h = time_end_to_end(cm, host_inputs, steps, warmup, flush)
     e2e_ms = group.max(statistics.mean(e2e_times), dev)
-    sep_times, _, _ = time_end_to_end(cm, host_inputs, max(20, steps // 4), warmup, flush, False)
-    sep_ms = group.max(statistics.mean(sep_times), dev)
 
     # batch 32 split over the ranks, independent replicas
     per_gpu = 32 // world
@@ -488,10 +474,7 @@ def run_ours(args) -> int:
                    "graph_branch_kernels": cm._streams.forked if cm._streams else 0,
                    "parallelism": f"{world} independent replicas, no collectives"},
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h,
-                "timing": "host wall clock around CompiledModel.run_host (copies and kernels in one "
-                          "graph launch, synchronised on return)",
-                "separate_copies_ms": round(sep_ms, 5)},
+                "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
         "gpu_launches": cm.generated_launches * steps,
         "clocks": clocks.summary(),
         "gpt2_small_fp16_b1_ms": round(gpt_ms, 5),

@@ -54,6 +54,10 @@ class Config:
     #: programmatic dependent launch of generated kernels: False, True (every
     #: launch) or "chain" (only behind another generated kernel on the same stream)
     dependent_launch: bool | str = "chain"
+    #: which kernels release their dependents at their top (``launch_dependents``):
+    #: 0 none, 1 launches that fit the machine in one wave, 2 all, 3 like 1 plus the
+    #: last wave of larger launches
+    dependent_trigger: int = 1
     #: pointwise kernels that move at least this many bytes use 256-bit global
     #: accesses (sm_100 ``ld/st.global.v4.b64``) when every operand allows it; 0 = never
     wide_access_bytes: int = 8 << 20

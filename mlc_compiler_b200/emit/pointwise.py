@@ -57,6 +57,21 @@ def single_wave(grid: int, block: int, sms: int = 148) -> bool:
     return grid * block <= sms * 1024
 
 
+def dependent_release(grid: int, block: int, cfg, indent: str = "    ") -> str | None:
+    """The line that releases the next launch (``griddepcontrol.launch_dependents``)
+    at the top of a kernel, or None.  ``Config.dependent_trigger``: 0 never;
+    1 launches that fit the machine in one wave; 2 every launch; 3 like 1, and in
+    larger launches only the CTAs of the last wave release (the rest do so by
+    exiting), so that the next grid is not set up before this one is all resident."""
+    policy = int(getattr(cfg, "dependent_trigger", 1))
+    if policy == 2 or (policy in (1, 3) and single_wave(grid, block)):
+        return f"{indent}MLCB_GRID_TRIGGER();"
+    if policy == 3:
+        last_wave = 148 * max(1, min(32, 2048 // block))
+        return f"{indent}if (blockIdx.x >= {grid - last_wave}u) MLCB_GRID_TRIGGER();"
+    return None
+
+
 def pick_vector(operands, numel: int, cap_bytes: int = 16) -> int:
     smallest = min((kir.ITEMSIZE[a.dtype] for a in operands), default=4)
     v = max(1, cap_bytes // smallest)
@@ -164,8 +179,8 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
         else:
             need_idx = True
 
-    if single_wave(grid, block):
-        L.append("    MLCB_GRID_TRIGGER();")
+    if dependent_release(grid, block, cfg):
+        L.append(dependent_release(grid, block, cfg))
     L.append("#pragma unroll")
     L.append(f"    for (int j = 0; j < {V}; ++j) {{")
     if need_idx:
@@ -360,8 +375,8 @@ def _emit_tiled(k: kir.PointwiseKernel, cfg, name: str, V: int, tile: Tile) -> t
                 L.append(f"    {rt} g{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + "
                          f"({render_offset(a.index, {'idx': 'base_idx'})}), g{i});  // {a.name}: along r only")
                 loads[i] = X.Val(f"g{i}[i]", vdt)
-    if single_wave(grid, block):
-        L.append("    MLCB_GRID_TRIGGER();")
+    if dependent_release(grid, block, cfg):
+        L.append(dependent_release(grid, block, cfg))
     L.append("#pragma unroll")
     L.append(f"    for (int i = 0; i < {V}; ++i) {{")
     L.append(f"        const {it} i0 = base_idx + i * {o_r};")

@@ -38,7 +38,7 @@ from ..kir import Bind, Reduce
 from . import expr as X
 from .indexing import (Access, check_bounds, classify, needs_64bit, pow2_ceil,
                        render_offset)
-from .pointwise import LaunchSpec, algorithmic_bytes, pick_vector, single_wave, store_code
+from .pointwise import LaunchSpec, algorithmic_bytes, pick_vector, dependent_release, store_code
 
 _OP = {"sum": "mlcb_op_sum", "prod": "mlcb_op_prod", "max": "mlcb_op_max", "min": "mlcb_op_min"}
 
@@ -472,8 +472,8 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
         c.emit("    }")
         if red is not None:
             _finish_reduce(c, red, acc_dt, rdt, reduces.index(red))
-        if ph == 0 and single_wave(geo.grid, geo.block):
-            c.emit("    MLCB_GRID_TRIGGER();")
+        if ph == 0 and dependent_release(geo.grid, geo.block, cfg):
+            c.emit(dependent_release(geo.grid, geo.block, cfg))
 
     _row_stores(c, loads)
     c.emit("}")
@@ -612,8 +612,8 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
     scalar_in = _scalar_loads(c)
     _row_offsets(c, k.inputs, "in")
     _row_offsets(c, k.outputs, "out")
-    if single_wave(geo.grid, geo.block):
-        c.emit("    MLCB_GRID_TRIGGER();")
+    if dependent_release(geo.grid, geo.block, cfg):
+        c.emit(dependent_release(geo.grid, geo.block, cfg))
 
     acc_in = {i: classify(a.index, "col", V) for i, a in enumerate(k.inputs)
               if a.index.varies_along("col")}

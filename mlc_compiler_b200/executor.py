@@ -172,9 +172,6 @@ class CompiledModel:
         self._static_inputs: list[torch.Tensor] | None = None
         self._graph_replay = None
         self._static_outputs: Any = None
-        self._host_graph: torch.cuda.CUDAGraph | None = None
-        self._host_in: list[torch.Tensor] = []
-        self._host_out: list[torch.Tensor] = []
         #: generated-kernel launches per forward (what a bench reports)
         self.generated_launches = len(self._exec.generated())
 
@@ -382,50 +379,6 @@ class CompiledModel:
             self.run_kernels(buffers)
         self._graph_replay = g
         self._static_outputs = self._collect(buffers)
-
-    def run_host(self, *inputs: torch.Tensor):
-        """The forward for callers whose data lives in host memory: ``inputs`` are
-        CPU tensors, the result is returned in pinned host memory and is valid on
-        return (the call synchronises).
-
-        One graph launch does everything: the inputs are copied into pinned staging
-        buffers owned by the model (a host memcpy of a few hundred bytes), and the
-        replayed graph holds the host-to-device copies from that staging area, the
-        schedule's kernels and the device-to-host copy of the outputs.  Compared
-        with ``compiled(*pinned)`` followed by a copy back, the device no longer
-        idles while the host issues each copy as a stream operation of its own.
-        The returned tensors are reused by the next call."""
-        if not (self.cfg.cuda_graphs and self.schedule.plan.mode == "arena"):
-            out = self.forward(*[t.to(self.device) for t in inputs])
-            outs = out if isinstance(out, tuple) else (out,)
-            host = tuple(o.cpu() for o in outs)
-            return host[0] if len(host) == 1 else host
-        self._check_inputs(inputs)
-        if self._host_graph is None:
-            self._capture_host(inputs)
-        for dst, src in zip(self._host_in, inputs):
-            dst.copy_(src.reshape(-1))
-        self._host_graph.replay()
-        torch.cuda.current_stream(self.device).synchronize()
-        return self._host_out[0] if len(self._host_out) == 1 else tuple(self._host_out)
-
-    def _capture_host(self, inputs) -> None:
-        if self._graph_replay is None:
-            # the device-side capture warms everything up (cuBLAS workspaces, modules)
-            self._capture([t.to(self.device) for t in inputs])
-        buffers = self._resident
-        outs = self._static_outputs if isinstance(self._static_outputs, tuple) \
-            else (self._static_outputs,)
-        self._host_in = [torch.empty(d.shape, dtype=d.dtype).pin_memory() for d in self._static_inputs]
-        self._host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for dst, src in zip(self._static_inputs, self._host_in):
-                dst.copy_(src, non_blocking=True)
-            self.run_kernels(buffers)
-            for dst, src in zip(self._host_out, outs):
-                dst.copy_(src, non_blocking=True)
-        self._host_graph = g
 
     def replay(self) -> None:
         """Replay the captured graph on the inputs already resident."""

@@ -242,28 +242,3 @@ def test_embeddings_gathered_by_the_layernorm_are_bit_identical(name, batch):
         ids = torch.randint(0, 30522, inputs[0].shape, generator=g)
         di = [ids.to(dev)] + [t.to(dev) for t in inputs[1:]]
         assert torch.equal(on(*di), off(*di))
-
-
-@pytest.mark.gpu
-def test_host_call_matches_the_device_call():
-    import torch
-    from mlc_compiler_b200 import Config, models
-    from mlc_compiler_b200.executor import CompiledModel
-    from mlc_compiler_b200.frontend import load_schedule
-
-    dev = torch.device("cuda", 0)
-    s = load_schedule("bert-base_b1_s128_float16")
-    model, inputs = models.build("bert-base", 1, dtype=torch.float16)
-    cm = CompiledModel(s, model, Config(), dev)
-    g = torch.Generator().manual_seed(5)
-    for _ in range(3):
-        ids = torch.randint(0, 30522, inputs[0].shape, generator=g)
-        host = cm.run_host(ids, *inputs[1:])
-        assert host.device.type == "cpu" and host.is_pinned()
-        got = host.clone()
-        want = cm(ids.to(dev), *[t.to(dev) for t in inputs[1:]]).cpu()
-        assert torch.equal(got, want)
-    with pytest.raises(Exception):
-        cm.run_host(ids[:, :5], *inputs[1:])
-    eager = CompiledModel(s, model, Config(cuda_graphs=False), dev)
-    assert torch.equal(eager.run_host(ids, *inputs[1:]), got)
