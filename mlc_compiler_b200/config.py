@@ -55,8 +55,9 @@ class Config:
     #: launch) or "chain" (only behind another generated kernel on the same stream)
     dependent_launch: bool | str = "chain"
     #: which kernels release their dependents at their top (``launch_dependents``):
-    #: 0 none, 1 launches that fit the machine in one wave, 2 all, 3 like 1 plus the
-    #: last wave of larger launches
+    #: 0 none, 1 launches that fit the machine in one wave, 2 all.  Measured: 0 costs the
+    #: small kernels 0.15-0.25 us per launch; 2 makes the 2.6-wave bias+GELU kernel 10 %
+    #: slower; releasing from the last wave only is no better than 1 and slower in the models
     dependent_trigger: int = 1
     #: pointwise kernels that move at least this many bytes use 256-bit global
     #: accesses (sm_100 ``ld/st.global.v4.b64``) when every operand allows it; 0 = never

@@ -60,15 +60,10 @@ def single_wave(grid: int, block: int, sms: int = 148) -> bool:
 def dependent_release(grid: int, block: int, cfg, indent: str = "    ") -> str | None:
     """The line that releases the next launch (``griddepcontrol.launch_dependents``)
     at the top of a kernel, or None.  ``Config.dependent_trigger``: 0 never;
-    1 launches that fit the machine in one wave; 2 every launch; 3 like 1, and in
-    larger launches only the CTAs of the last wave release (the rest do so by
-    exiting), so that the next grid is not set up before this one is all resident."""
+    1 launches that fit the machine in one wave; 2 every launch."""
     policy = int(getattr(cfg, "dependent_trigger", 1))
-    if policy == 2 or (policy in (1, 3) and single_wave(grid, block)):
+    if policy == 2 or (policy == 1 and single_wave(grid, block)):
         return f"{indent}MLCB_GRID_TRIGGER();"
-    if policy == 3:
-        last_wave = 148 * max(1, min(32, 2048 // block))
-        return f"{indent}if (blockIdx.x >= {grid - last_wave}u) MLCB_GRID_TRIGGER();"
     return None
 
 
