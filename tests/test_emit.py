@@ -171,3 +171,67 @@ def test_example_compiles_against_the_device_header(tmp_path):
     cmd = [B.nvcc_path(), *B.GENCODE, *B.NVCC_FLAGS, "-cubin", "-o", str(out), str(B.EXAMPLE)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+# ---- counterparts of the reference's checks on generated source -----------------
+# (``tests/test_reduction_fusion.py:284-330`` and ``tests/test_dtypes.py:61-69`` read
+# the Triton text; these read the CUDA text for the same properties)
+
+def _softmax_kernel(stem):
+    from conftest import load_tiny
+    s = load_tiny(stem)["schedule"]
+    k = next(k for k in s.generated() if isinstance(k, kir.ReductionKernel))
+    return generate_module(s, Config()).kernel_source(k.name)
+
+
+def test_persistent_source_has_no_column_loop_and_streamed_rescales():
+    persistent = _softmax_kernel("oddsm100__default__float32")
+    assert "c0 +=" not in persistent                      # the row is read once, into registers
+    assert "mlcb_op_max" in persistent and "mlcb_op_sum" in persistent
+    streamed = _softmax_kernel("oddsm1000__streamed__float32")
+    assert streamed.count("c0 += 128") == 2                # max+sum in one pass, then the store pass
+    assert "run_l * ((run_m == MLCB_NINF_F) ? 0.0f : expf(run_m - nm))" in streamed
+    assert "if (nm != MLCB_NINF_F)" in streamed            # a fully masked chunk cannot produce NaN
+
+
+def test_dead_lanes_contribute_the_identity_of_the_reduction():
+    # 100 columns over 32 lanes x 4: lanes 25..31 hold nothing; the max must see -inf
+    # there (not a zero fill) and the sum must see 0
+    src = _softmax_kernel("oddsm100__default__float32")
+    assert "float acc_r2 = MLCB_NINF_F;" in src and "float acc_r5 = ((float)0);" in src
+    body = src[src.index("float acc_r2"):src.index("const float r2")]
+    assert "if (c0 < 100) {" in body                       # dead lanes never touch the accumulator
+    assert body.index("if (c0 < 100)") < body.index("acc_r2 = mlcb_op_max")
+
+
+def test_row_statistics_load_as_scalars():
+    rows, cols = 6, 32
+    rc = kir.IndexMap((kir.Axis("row", rows, ((rows, 1, cols),)), kir.Axis("col", cols, ((cols, 1, 1),))))
+    r = kir.IndexMap((kir.Axis("row", rows, ((rows, 1, 1),)), kir.Axis("col", cols, ())))
+    k = kir.ReductionKernel(
+        "k0", (rows,), (cols,),
+        [kir.Operand("x", "x", "float32", rc), kir.Operand("rowbias", "rowbias", "float32", r)],
+        [kir.Operand("y", "y", "float32", kir.IndexMap((kir.Axis("row", rows, ((rows, 1, 1),)),)))],
+        [kir.Reduce("r0", "max", kir.Load(0)),
+         kir.Bind("t1", kir.Call("exp", (kir.Call("sub", (kir.Load(0), kir.Ref("r0"))),))),
+         kir.Reduce("r2", "sum", kir.Ref("t1")),
+         kir.Bind("t3", kir.Call("mul", (kir.Ref("r2"), kir.Load(1))))],
+        {"y": kir.Ref("t3")}, {"y"}, False, ["amax", "sub", "exp", "sum", "mul"])
+    from mlc_compiler_b200.emit.reduction import emit_reduction
+    src, _ = emit_reduction(k, Config())
+    scalar = [l for l in src.splitlines() if "mlcb_load1" in l]
+    assert len(scalar) == 1 and "(per row)" in scalar[0] and "c0" not in scalar[0]
+    assert "v1[" not in src                                # no register array for the per-row operand
+    assert "if (live && lane == 0) mlcb_store1<float>(out0 + (row)" in src
+
+
+def test_narrow_loads_widen_and_stores_round_back():
+    from conftest import load_tiny
+    s = load_tiny("layernorm_scale__default__float16")["schedule"]
+    src = generate_module(s, Config(), inline_header=False).source     # kernels only, no device library
+    loads = [l for l in src.splitlines() if "mlcb_load<" in l]
+    assert loads and all("mlcb_load<__half," in l for l in loads)
+    arrays = [l for l in src.splitlines() if l.strip().startswith(("float v", "__half v"))]
+    assert arrays and all(l.strip().startswith("float v") for l in arrays)   # registers hold fp32
+    stores = [l for l in src.splitlines() if "mlcb_store<" in l]
+    assert stores and all("mlcb_store<__half," in l for l in stores)
