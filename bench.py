@@ -471,6 +471,7 @@ def run_ours(args) -> int:
                    "arena_kib": round(sched.arena_bytes / 1024, 1),
                    "l2": "flushed between steps (256 MiB write)",
                    "graph_streams": cm.cfg.graph_streams, "dependent_launch": cm.cfg.dependent_launch,
+                   "dependent_policy_chosen": cm.dependent_policy,
                    "graph_branch_kernels": cm._streams.forked if cm._streams else 0,
                    "parallelism": f"{world} independent replicas, no collectives"},
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,

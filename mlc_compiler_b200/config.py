@@ -52,8 +52,9 @@ class Config:
     #: division (error ~1e-6, below half-precision resolution); fp32 kernels never do
     narrow_fast_math: bool = True
     #: programmatic dependent launch of generated kernels: False, True (every
-    #: launch) or "chain" (only behind another generated kernel on the same stream)
-    dependent_launch: bool | str = "chain"
+    #: launch), "chain" (only behind another generated kernel on the same stream) or
+    #: "auto" (the executor captures the graph both ways, times them, keeps the faster)
+    dependent_launch: bool | str = "auto"
     #: which kernels release their dependents at their top (``launch_dependents``):
     #: 0 none, 1 launches that fit the machine in one wave, 2 all.  Measured: 0 costs the
     #: small kernels 0.15-0.25 us per launch; 2 makes the 2.6-wave bias+GELU kernel 10 %

@@ -282,10 +282,10 @@ class CudaRuntime:
             torch.cuda.current_stream()  # makes sure the primary context exists
             self.loaded = LoadedModule(compile_source(self.source), index)
         self.lib = self.loaded.lib
-        # "chain" is resolved per launch by an executor that knows the stream order;
+        # "chain" and "auto" are resolved per launch by an executor that knows the stream order;
         # a host that binds kernels one by one gets plain launches
         self.flags = 1 if getattr(cfg, "dependent_launch", False) is True else 0
-        self.chain = getattr(cfg, "dependent_launch", False) == "chain"
+        self.chain = getattr(cfg, "dependent_launch", False) in ("chain", "auto")
 
     @staticmethod
     def _is_extern(k) -> bool:

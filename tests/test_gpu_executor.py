@@ -242,3 +242,29 @@ def test_embeddings_gathered_by_the_layernorm_are_bit_identical(name, batch):
         ids = torch.randint(0, 30522, inputs[0].shape, generator=g)
         di = [ids.to(dev)] + [t.to(dev) for t in inputs[1:]]
         assert torch.equal(on(*di), off(*di))
+
+
+@pytest.mark.gpu
+def test_auto_dependent_launch_keeps_the_faster_graph_and_the_same_answer():
+    import torch
+    from mlc_compiler_b200 import Config, models
+    from mlc_compiler_b200.executor import CompiledModel
+    from mlc_compiler_b200.frontend import load_schedule
+
+    dev = torch.device("cuda", 0)
+    s = load_schedule("bert-base_b1_s128_float16")
+    model, inputs = models.build("bert-base", 1, dtype=torch.float16)
+    di = [t.to(dev) for t in inputs]
+    auto = CompiledModel(s, model, Config(), dev)
+    assert auto.cfg.dependent_launch == "auto" and auto.dependent_policy is None
+    a = auto(*di).clone()
+    assert auto.dependent_policy in ("chain", True)
+    assert set(auto.policy_timings_ms) == {"chain", "True"}
+    chosen, other = auto.policy_timings_ms[str(auto.dependent_policy)], \
+        auto.policy_timings_ms["True" if auto.dependent_policy == "chain" else "chain"]
+    assert chosen <= other * 1.006
+    for policy in ("chain", True, False):
+        fixed = CompiledModel(s, model, Config(dependent_launch=policy), dev)
+        assert torch.equal(fixed(*di), a)
+        assert fixed.dependent_policy is None
+    assert torch.equal(auto(*di), a)                 # replays of the kept graph
