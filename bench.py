@@ -364,7 +364,8 @@ def run_ours(args) -> int:
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
     cfg_kw = dict(kv.split("=") for kv in args.cfg)
-    cfg_kw = {k: (v == "True" if v in ("True", "False") else int(v)) for k, v in cfg_kw.items()}
+    cfg_kw = {k: (v == "True" if v in ("True", "False") else int(v) if v.lstrip("-").isdigit() else v)
+              for k, v in cfg_kw.items()}
     if args.section == "families":
         fcm, fin, fs = _compiled(args.model, args.batch, getattr(torch, args.dtype), dev, **cfg_kw)
         fdev = [t.to(dev) for t in fin]
