@@ -477,7 +477,8 @@ def run_ours(args) -> int:
                    "parallelism": f"{world} independent replicas, no collectives"},
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
-        "gpu_launches": cm.generated_launches * steps,
+        # generated kernels launched inside the timed region, all ranks together
+        "gpu_launches": cm.generated_launches * steps * world,
         "clocks": clocks.summary(),
         "gpt2_small_fp16_b1_ms": round(gpt_ms, 5),
         "timed_region_wall_s": round(wall, 3),
