@@ -71,6 +71,10 @@ class Config:
     #: let a matmul store straight into the layout a following pure copy would have
     #: produced (the context ``clone`` at batch 1); same op, same values, one launch fewer
     write_through_copies: bool = True
+    #: at batch > 1 store the operands and result of the attention ``bmm`` calls
+    #: sequence-first, which makes ``(batch, head)`` one strided dimension: the context
+    #: ``clone`` disappears and the key copy stops transposing
+    sequence_first: bool = True
     #: fetch embedding rows inside the row reduction that consumes them instead of
     #: through a separate library gather (same table entries, bit-identical)
     fold_embeddings: bool = True

@@ -721,6 +721,304 @@ def fold_embeddings(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule
     return _replanned(out) if replan else out
 
 
+# --------------------------------------------------------------------------
+# batch > 1: sequence-first storage around the attention matmuls
+# --------------------------------------------------------------------------
+
+_ROWWISE = {"aten.mm.default": 0, "aten.addmm.default": 1}      # op -> position of the row operand
+
+
+def _whole_dense(schedule, v) -> bool:
+    return (isinstance(v, kir.View) and v.offset == 0 and v.strides == _dense_strides(v.shape)
+            and v.numel == schedule.buffers[v.buffer].numel)
+
+
+def _movable(schedule, buffer: str, finals) -> bool:
+    return buffer not in finals and schedule.buffers[buffer].plannable
+
+
+def output_major(k: kir.PointwiseKernel) -> kir.PointwiseKernel:
+    """``k`` iterating in the order its first output is stored.
+
+    A pointwise kernel may visit its elements in any order.  The frontend numbers
+    them by the output's *logical* shape; once a buffer has been given another
+    physical layout that numbering can leave no operand contiguous along the
+    innermost iteration digit, and the emitter would fall back to one element per
+    access.  The iteration index is cut at every boundary any operand's map uses,
+    the resulting digits are re-ordered by the output's stride, and every map is
+    rewritten for the new numbering (adjacent digits an operand walks densely are
+    fused again)."""
+    operands = list(k.inputs) + list(k.outputs)
+    if not k.outputs or any(len(a.index.axes) != 1 or a.via is not None for a in operands):
+        return k
+    numel = k.numel
+    cuts = {1, numel}
+    for a in operands:
+        for n, o, _ in a.index.axes[0].terms:
+            cuts.add(o)
+            cuts.add(o * n)
+    edges = sorted(cuts)
+    if any(hi % lo for lo, hi in zip(edges, edges[1:])):
+        return k
+    digits = [(hi // lo, lo) for lo, hi in zip(edges, edges[1:])]          # (size, weight), innermost first
+
+    def strides(a):
+        out = []
+        for size, lo in digits:
+            st = 0
+            for n, o, s_ in a.index.axes[0].terms:
+                if o <= lo and lo * size <= o * n and lo % o == 0:
+                    st = s_ * (lo // o)
+            out.append(st)
+        return out
+
+    key = strides(k.outputs[0])
+    if any(st == 0 for st in key):
+        return k
+    order = sorted(range(len(digits)), key=lambda j: key[j])                # innermost first
+    if order == list(range(len(digits))):
+        return k
+    weight, w = {}, 1
+    for j in order:
+        weight[j] = w
+        w *= digits[j][0]
+
+    def rebuilt(a):
+        st = strides(a)
+        terms = []                                                          # innermost first
+        for j in order:
+            n, sj = digits[j][0], st[j]
+            if sj == 0:
+                continue
+            if terms and terms[-1][1] * terms[-1][0] == weight[j] and terms[-1][2] * terms[-1][0] == sj:
+                terms[-1] = (terms[-1][0] * n, terms[-1][1], terms[-1][2])
+            else:
+                terms.append((n, weight[j], sj))
+        return kir.Operand(a.name, a.buffer, a.dtype, kir.IndexMap(
+            (kir.Axis(a.index.axes[0].var, numel, tuple(reversed(terms))),), a.index.base))
+
+    space = tuple(digits[j][0] for j in reversed(order))
+    return kir.PointwiseKernel(k.name, space, [rebuilt(a) for a in k.inputs],
+                               [rebuilt(a) for a in k.outputs], k.body, k.out_expr, k.ops)
+
+
+def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
+    """Store the operands and the result of the attention ``bmm`` calls as
+    ``[T, B, H, D/H]`` instead of ``[B, H, T, D/H]`` when the batch is larger
+    than one.
+
+    ``bmm`` has one batch dimension with one stride.  With tokens stored
+    batch-first the merged layout ``[B, T, H, D/H]`` the output projection wants
+    has no such stride for ``(b, h)``, which is why the exporter puts a ``clone``
+    after the context matmul (and transposing clones in front of it).  With
+    tokens stored sequence-first, ``(b, h)`` is contiguous with stride ``D/H``
+    both in the head layout and in the merged layout: ``bmm`` reads and writes
+    ``[T, B, H, D/H]`` through plain strided views, the context ``clone`` becomes
+    the identity and disappears (``read_through_copies``), and the key copy no
+    longer transposes.  The output projection then sees its rows in ``(t, b)``
+    order -- a matmul treats rows independently -- and the generated kernel that
+    consumes its result reads row ``(b, t)`` at ``(t B + b)``.  Only buffers
+    between the head copies and that kernel move; every index map and view on
+    them is rewritten with ``layout.remap``, and a buffer whose uses cannot all be
+    rewritten keeps its layout."""
+    from . import layout as L
+
+    kernels = list(schedule.kernels)
+    finals = {v.buffer for v in schedule.outputs}
+    writer = {}
+    for k in kernels:
+        for b in k.writes():
+            writer.setdefault(b, []).append(k)
+
+    # anchor: bmm -> pure copy -> row operand of a matmul
+    anchor = None
+    for k in kernels:
+        if not (isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1):
+            continue
+        a = k.args[_ROWWISE[k.op]]
+        if not (_whole_dense(schedule, a) and len(a.shape) == 2):
+            continue
+        w = writer.get(a.buffer, [])
+        if len(w) != 1 or not _pure_copy(w[0]):
+            continue
+        src = writer.get(w[0].inputs[0].buffer, [])
+        if len(src) != 1 or not (isinstance(src[0], kir.ExternKernel) and src[0].op == "aten.bmm.default"):
+            continue
+        ctx = src[0].outputs[0]
+        if not (_whole_dense(schedule, ctx) and len(ctx.shape) == 3 and ctx.numel == a.numel):
+            continue
+        G, T, Dh = ctx.shape
+        R, F = a.shape
+        if F % Dh or G % (F // Dh) or (G // (F // Dh)) * T != R:
+            continue
+        anchor = (G // (F // Dh), T, F // Dh)
+        break
+    if anchor is None or anchor[0] == 1:
+        return schedule
+    B, T, H = anchor
+
+    tables: dict[str, list] = {}
+
+    def propose(buffer, digits):
+        if not _movable(schedule, buffer, finals):
+            return
+        if buffer in tables and tables[buffer] != digits:
+            tables[buffer] = None                                # two roles, two layouts: leave it
+        else:
+            tables.setdefault(buffer, digits)
+
+    for k in kernels:
+        if not isinstance(k, kir.ExternKernel):
+            continue
+        if k.op == "aten.bmm.default":
+            for v in list(k.args[:2]) + list(k.outputs):
+                if not (_whole_dense(schedule, v) and len(v.shape) == 3):
+                    continue
+                G, M, N = v.shape
+                if G != B * H or (M == T) == (N == T):
+                    continue
+                order = (2, 0, 1, 3) if M == T else (3, 0, 1, 2)
+                propose(v.buffer, L.dense_digits((B, H, M, N), order))
+    # matmuls fed by a copy of a moved bmm result: row operand and result move together
+    for k in kernels:
+        if isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1:
+            a, out = k.args[_ROWWISE[k.op]], k.outputs[0]
+            if not (_whole_dense(schedule, a) and _whole_dense(schedule, out) and len(a.shape) == 2
+                    and a.shape[0] == B * T and out.shape[0] == B * T):
+                continue
+            w = writer.get(a.buffer, [])
+            if len(w) == 1 and _pure_copy(w[0]) and tables.get(w[0].inputs[0].buffer):
+                propose(a.buffer, L.dense_digits((B, T, a.shape[1]), (1, 0, 2)))
+                propose(out.buffer, L.dense_digits((B, T, out.shape[1]), (1, 0, 2)))
+    tables = {b: d for b, d in tables.items() if d}
+
+    def rowwise_pair(k):
+        if isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1:
+            return k.args[_ROWWISE[k.op]], k.outputs[0]
+        return None
+
+    def rewrite_kernel(k):
+        """``k`` with every use of a moved buffer re-addressed (raises NoRemap)."""
+        if isinstance(k, kir.ExternKernel):
+            pair = rowwise_pair(k)
+            keep = set()
+            if pair and pair[0].buffer in tables and pair[1].buffer in tables \
+                    and _whole_dense(schedule, pair[0]) and _whole_dense(schedule, pair[1]):
+                keep = {id(pair[0]), id(pair[1])}                # rows permuted on both sides
+
+            def fix(a):
+                if isinstance(a, kir.View):
+                    if a.buffer in tables and id(a) not in keep:
+                        return L.remap_view(a, a.buffer, tables[a.buffer])
+                    return a
+                if isinstance(a, (list, tuple)):
+                    return type(a)(fix(x) for x in a)
+                return a
+            if pair and not keep and (pair[0].buffer in tables) != (pair[1].buffer in tables):
+                raise L.NoRemap("row operand and result of a matmul must move together")
+            return kir.ExternKernel(k.name, k.op, [fix(a) for a in k.args],
+                                    {n: fix(a) for n, a in k.kwargs.items()},
+                                    [fix(o) for o in k.outputs])
+        touched = [a for a in list(k.inputs) + list(k.outputs) if a.buffer in tables]
+        if not touched:
+            return k
+
+        def op(a):
+            if a.buffer not in tables:
+                return a
+            if a.via is not None:
+                raise L.NoRemap("gathered operand")
+            return kir.Operand(a.name, a.buffer, a.dtype, L.remap_index(a.index, tables[a.buffer]))
+        if isinstance(k, kir.PointwiseKernel):
+            return output_major(kir.PointwiseKernel(k.name, k.space, [op(a) for a in k.inputs],
+                                                    [op(a) for a in k.outputs], k.body, k.out_expr,
+                                                    k.ops))
+        return kir.ReductionKernel(k.name, k.row_space, k.reduce_space, [op(a) for a in k.inputs],
+                                   [op(a) for a in k.outputs], k.steps, k.out_expr, k.row_outputs,
+                                   k.two_pass, k.ops)
+
+    # a buffer whose uses cannot all be re-addressed keeps its layout; so does its partner
+    for _ in range(len(tables) + 1):
+        bad = None
+        for k in kernels:
+            try:
+                rewrite_kernel(k)
+            except L.NoRemap:
+                used = [b for b in list(k.reads()) + list(k.writes()) if b in tables]
+                bad = used
+                break
+        if bad is None:
+            break
+        for b in bad:
+            tables.pop(b, None)
+    else:
+        return schedule
+    if not tables:
+        return schedule
+    out = kir.Schedule(name=schedule.name, kernels=[rewrite_kernel(k) for k in kernels],
+                       buffers=schedule.buffers, inputs=schedule.inputs, outputs=schedule.outputs,
+                       params=schedule.params, plan=schedule.plan, meta=dict(schedule.meta))
+    return _replanned(out) if replan else out
+
+
+def read_through_copies(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
+    """Drop a pure copy whose result is only read by library calls, by pointing
+    their views at the copy's source (the input-side twin of
+    ``write_through_copies``).  After ``sequence_first`` the context ``clone`` is
+    such a copy, and an identity at that."""
+    from . import layout as L
+
+    kernels: list = list(schedule.kernels)
+    finals = {v.buffer for v in schedule.outputs}
+    dropped = False
+    for ci, c in enumerate(kernels):
+        if c is None or not _pure_copy(c):
+            continue
+        x, y = c.inputs[0], c.outputs[0]
+        if y.buffer in finals or not schedule.buffers[y.buffer].plannable:
+            continue
+        users = [ki for ki, k in enumerate(kernels) if k is not None and ki != ci
+                 and (y.buffer in k.reads() or y.buffer in k.writes())]
+        if not users or min(users) < ci or not all(
+                isinstance(kernels[ki], kir.ExternKernel) and y.buffer not in kernels[ki].writes()
+                for ki in users):
+            continue
+        if any(k is not None and x.buffer in k.writes() for k in kernels[ci + 1:max(users) + 1]):
+            continue
+        try:
+            src = kir.IndexMap(x.index.axes, 0)
+            digits = L.copy_digits(src, y.index, forward=False)
+
+            def fix(a):
+                if isinstance(a, kir.View):
+                    if a.buffer != y.buffer:
+                        return a
+                    v = L.remap_view(a, x.buffer, digits)
+                    v = kir.View(v.name, v.buffer, v.shape, v.strides, v.offset + x.index.base)
+                    if len(v.shape) >= 2 and not _blas_layout(v.shape, v.strides):
+                        raise L.NoRemap("not a matrix a BLAS call takes without copying")
+                    return v
+                if isinstance(a, (list, tuple)):
+                    return type(a)(fix(e) for e in a)
+                return a
+            new = {ki: kir.ExternKernel(kernels[ki].name, kernels[ki].op,
+                                        [fix(a) for a in kernels[ki].args],
+                                        {n: fix(a) for n, a in kernels[ki].kwargs.items()},
+                                        list(kernels[ki].outputs)) for ki in users}
+        except L.NoRemap:
+            continue
+        for ki, k in new.items():
+            kernels[ki] = k
+        kernels[ci] = None
+        dropped = True
+    if not dropped:
+        return schedule
+    out = kir.Schedule(name=schedule.name, kernels=[k for k in kernels if k is not None],
+                       buffers=schedule.buffers, inputs=schedule.inputs, outputs=schedule.outputs,
+                       params=schedule.params, plan=schedule.plan, meta=dict(schedule.meta))
+    return _replanned(out) if replan else out
+
+
 def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
     """Every rewrite ``cfg`` enables, in the order the executor applies them.
     Only arena-planned schedules are rewritten: the rewrites change live ranges
@@ -730,6 +1028,10 @@ def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
     work = schedule
     if getattr(cfg, "bias_epilogue", False):
         work = fold_bias_into_matmul(work)
+    if getattr(cfg, "sequence_first", True):
+        moved = sequence_first(work)
+        if moved is not work:
+            work = read_through_copies(moved)
     if getattr(cfg, "forward_into_copies", True):
         work = forward_into_consumers(work)
     if getattr(cfg, "write_through_copies", True):

@@ -241,3 +241,70 @@ def test_embedding_with_other_readers_stays_a_library_call():
                      s.params, s.plan, dict(s.meta))
     r = rewrite.fold_embeddings(t, replan=False)
     assert emb.name in {k.name for k in r.kernels} and len(t) - len(r) == 1
+
+
+# ---- sequence-first storage around the attention matmuls ------------------------
+
+@pytest.mark.parametrize("name,batch,before,after", [("bert-base", 4, 236, 184), ("gpt2-small", 4, 184, 158)])
+def test_sequence_first_removes_the_context_clone_at_batch_above_one(name, batch, before, after):
+    s = load_schedule(models.schedule_name(name, batch, torch.float16))
+    moved = rewrite.sequence_first(s)
+    assert moved is not s and len(moved) == len(s) == before
+    r = rewrite.read_through_copies(moved)
+    assert len(moved) - len(r) == 12
+    B, T, D, Dh = batch, 128, 768, 64
+    bmms = [k for k in r.kernels if isinstance(k, kir.ExternKernel) and k.op == "aten.bmm.default"]
+    scores, context = bmms[0], bmms[1]
+    assert scores.args[0].strides == (Dh, B * D, 1)              # queries, [T, B, H, Dh]
+    assert scores.args[1].strides == (Dh, 1, B * D)              # keys, same storage, transposed view
+    assert context.outputs[0].strides == (Dh, B * D, 1)          # written where the projection reads
+    proj = r.kernels[r.kernels.index(context) + 1]
+    assert proj.op == "aten.mm.default" and proj.args[0].buffer == context.outputs[0].buffer
+    assert proj.args[0].strides == (D, 1)
+    # no copy transposes any more: the three head copies are one function of the emitter
+    full = rewrite.prepare(s, Config())
+    assert len(full) == after
+    copies = [k for k in full.generated() if isinstance(k, kir.PointwiseKernel) and "clone" in k.ops]
+    assert len(copies) == 36 and all(k.outputs[0].index.axes[0].terms == ((k.numel, 1, 1),) for k in copies)
+    from mlc_compiler_b200.emit import generate_module
+    mod = generate_module(full, Config())
+    assert len({mod.symbol[k.name] for k in copies}) == (1 if name == "bert-base" else 3)
+    assert all(mod.launch[k.name].vector >= 8 for k in copies)
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    a, _ = oracle.run_schedule(s, model, inputs)
+    b, _ = oracle.run_schedule(full, model, inputs)
+    assert torch.equal(a, b)
+
+
+def test_sequence_first_leaves_batch_one_and_plain_models_alone():
+    s = load_schedule("bert-base_b1_s128_float16")
+    assert rewrite.sequence_first(s) is s
+    s = load_schedule("micro-softmax_b8_s128_float16")
+    assert rewrite.sequence_first(s) is s
+
+
+@pytest.mark.parametrize("stem", [c for c in tiny_cases() if c.startswith(("block", "attention"))])
+def test_prepare_never_changes_tiny_model_outputs(stem):
+    d = load_tiny(stem)
+    s = d["schedule"]
+    r = rewrite.prepare(s, Config())
+    a, _ = oracle.run_schedule(s, d["params"], d["inputs"])
+    b, _ = oracle.run_schedule(r, d["params"], d["inputs"])
+    assert torch.equal(a, b)
+
+
+def test_output_major_iteration_by_enumeration():
+    # a key copy after the move: iteration (B, H, Dh, T), output stored [T, B, H, Dh]
+    B, H, Dh, T = 2, 3, 4, 5
+    D, n = H * Dh, B * H * Dh * T
+    src = _ax(n, (B, H * Dh * T, T * D), (H * Dh, T, 1), (T, 1, D))
+    dst = _ax(n, (B, H * Dh * T, D), (H, Dh * T, Dh), (Dh, T, 1), (T, 1, B * D))
+    k = kir.PointwiseKernel("k", (B, H, Dh, T), [kir.Operand("x", "x", "float32", src)],
+                            [kir.Operand("y", "y", "float32", dst)], [], {"y": kir.Load(0)}, ["clone"])
+    r = rewrite.output_major(k)
+    assert r.space == (T, B, H * Dh) or r.space == (T, B, H, Dh)
+    assert r.outputs[0].index.axes[0].terms == ((n, 1, 1),)
+    pairs = {(k.inputs[0].index.offset(idx=i), k.outputs[0].index.offset(idx=i)) for i in range(n)}
+    again = {(r.inputs[0].index.offset(idx=i), r.outputs[0].index.offset(idx=i)) for i in range(n)}
+    assert pairs == again and len(pairs) == n
+    assert rewrite.output_major(r) is r
