@@ -879,6 +879,29 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
                     continue
                 order = (2, 0, 1, 3) if M == T else (3, 0, 1, 2)
                 propose(v.buffer, L.dense_digits((B, H, M, N), order))
+    # a generated kernel's result that only feeds pure copies into moved bmm operands
+    # (the bias add in front of the head copies): stored [T, B, H, J, D/H] -- J = 3 for a
+    # fused q/k/v projection -- (b, h) is one stride for each of the J slices, the
+    # copies become re-addressable and ``read_through_copies`` drops them
+    readers: dict[str, list] = {}
+    for k in kernels:
+        for b in k.reads():
+            readers.setdefault(b, []).append(k)
+    for y in [b for b, d in tables.items() if d]:
+        w = writer.get(y, [])
+        if len(w) != 1 or not _pure_copy(w[0]):
+            continue
+        x = w[0].inputs[0].buffer
+        spec = schedule.buffers[x]
+        made = writer.get(x, [])
+        if (x in tables or len(made) != 1 or isinstance(made[0], kir.ExternKernel)
+                or spec.numel % (B * T * H) or not all(
+                    _pure_copy(r) and tables.get(r.outputs[0].buffer) for r in readers.get(x, []))):
+            continue
+        Dh = schedule.buffers[y].numel // (B * T * H)
+        J, rem = divmod(spec.numel, B * T * H * Dh)
+        if rem == 0 and J >= 1:
+            propose(x, L.dense_digits((B, T, J, H, Dh), (1, 0, 3, 2, 4)))
     # matmuls fed by a copy of a moved bmm result: row operand and result move together
     for k in kernels:
         if isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1:

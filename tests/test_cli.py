@@ -24,4 +24,4 @@ def test_source_of_an_extern_kernel_is_refused(capsys):
 def test_rewritten_view_shows_forwarded_producers(capsys):
     assert main(["show", "bert-base_b8_s128_float16", "--rewritten"]) == 0
     out = capsys.readouterr().out
-    assert "schedule(184 kernels" in out and "[add, clone]" in out and "[embedding, embedding" in out
+    assert "schedule(184 kernels" in out and "clone" not in out and "[embedding, embedding" in out

@@ -284,7 +284,7 @@ def test_sequence_first_attention_storage_gives_the_same_answer(name, batch):
     di = [t.to(dev) for t in inputs]
     on = CompiledModel(s, model, Config(), dev)
     off = CompiledModel(s, model, Config(sequence_first=False), dev)
-    assert len(off.executed_schedule) - len(on.executed_schedule) == 12
+    assert len(off.executed_schedule) - len(on.executed_schedule) == (12 if name == "bert-base" else 36)
     for _ in range(3):
         a, b = on(*di).float(), off(*di).float()
     torch.cuda.synchronize()
