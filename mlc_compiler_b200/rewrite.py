@@ -894,14 +894,25 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
         x = w[0].inputs[0].buffer
         spec = schedule.buffers[x]
         made = writer.get(x, [])
-        if (x in tables or len(made) != 1 or isinstance(made[0], kir.ExternKernel)
-                or spec.numel % (B * T * H) or not all(
-                    _pure_copy(r) and tables.get(r.outputs[0].buffer) for r in readers.get(x, []))):
+        if (x in tables or len(made) != 1 or spec.numel % (B * T * H) or not all(
+                _pure_copy(r) and tables.get(r.outputs[0].buffer) for r in readers.get(x, []))):
             continue
         Dh = schedule.buffers[y].numel // (B * T * H)
         J, rem = divmod(spec.numel, B * T * H * Dh)
-        if rem == 0 and J >= 1:
+        if rem or J < 1:
+            continue
+        if not isinstance(made[0], kir.ExternKernel):
             propose(x, L.dense_digits((B, T, J, H, Dh), (1, 0, 3, 2, 4)))
+        elif J == 1 and made[0].op in _ROWWISE and len(made[0].outputs) == 1:
+            # written by a matmul itself (bias folded into it): a library call cannot
+            # interleave columns, but its rows can come in (t, b) order if its row
+            # operand does
+            a, out = made[0].args[_ROWWISE[made[0].op]], made[0].outputs[0]
+            if (_whole_dense(schedule, a) and _whole_dense(schedule, out) and len(a.shape) == 2
+                    and a.shape[0] == B * T and not any(
+                        isinstance(w_, kir.ExternKernel) for w_ in writer.get(a.buffer, []))):
+                propose(x, L.dense_digits((B, T, out.shape[1]), (1, 0, 2)))
+                propose(a.buffer, L.dense_digits((B, T, a.shape[1]), (1, 0, 2)))
     # matmuls fed by a copy of a moved bmm result: row operand and result move together
     for k in kernels:
         if isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1:
