@@ -313,3 +313,18 @@ def test_output_major_iteration_by_enumeration():
     again = {(r.inputs[0].index.offset(idx=i), r.outputs[0].index.offset(idx=i)) for i in range(n)}
     assert pairs == again and len(pairs) == n
     assert rewrite.output_major(r) is r
+
+
+def test_bias_epilogue_and_sequence_first_compose():
+    s = load_schedule(models.schedule_name("bert-base", 4, torch.float16))
+    model, inputs = models.build("bert-base", 4, dtype=torch.float16)
+    _with_random_biases(model)
+    full = rewrite.prepare(s, Config(bias_epilogue=True))
+    # the same launches batch 1 runs with the bias folded into the matmuls
+    one = rewrite.prepare(load_schedule(models.schedule_name("bert-base", 1, torch.float16)),
+                          Config(bias_epilogue=True))
+    assert len(full) == len(one) == 148
+    assert not any(isinstance(k, kir.PointwiseKernel) and "clone" in k.ops for k in full.kernels)
+    a, _ = oracle.run_schedule(s, model, inputs)
+    b, _ = oracle.run_schedule(full, model, inputs)
+    assert (a.float() - b.float()).abs().max().item() <= 1e-2
