@@ -937,8 +937,10 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
             pair = rowwise_pair(k)
             keep = set()
             if pair and pair[0].buffer in tables and pair[1].buffer in tables \
-                    and _whole_dense(schedule, pair[0]) and _whole_dense(schedule, pair[1]):
-                keep = {id(pair[0]), id(pair[1])}                # rows permuted on both sides
+                    and _whole_dense(schedule, pair[0]) and _whole_dense(schedule, pair[1]) \
+                    and all(len(v.shape) == 2 and v.shape[0] == B * T and tables[v.buffer] ==
+                            L.dense_digits((B, T, v.shape[1]), (1, 0, 2)) for v in pair):
+                keep = {id(pair[0]), id(pair[1])}                # the same row permutation on both sides
 
             def fix(a):
                 if isinstance(a, kir.View):
