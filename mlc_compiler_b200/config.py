@@ -94,6 +94,14 @@ class Config:
     def replace(self, **kw) -> "Config":
         return _replace(self, **kw)
 
+    def as_scheduled(self) -> "Config":
+        """The same configuration with every executor-side rewrite off: the schedule
+        runs kernel for kernel and library call for library call as the frontend
+        produced it, on one stream."""
+        return _replace(self, forward_into_copies=False, write_through_copies=False,
+                        sequence_first=False, fold_embeddings=False, bias_epilogue=False,
+                        graph_streams=1, dependent_launch="chain")
+
 
 NO_FUSION = Config(elementwise_fusion=False, recompute=False, reduction_fusion=False,
                    memory_planning=False, cuda_graphs=False)

@@ -67,8 +67,7 @@ def test_kernels_never_write_outside_their_arena_slices(dev):
         live_end[n] = shifted.plan.offsets[n] + s.buffers[n].nbytes
     shifted.plan.arena_bytes = s.plan.arena_bytes * 2 + 2 * pad + 4096
     cm = CompiledModel(shifted, d["params"],
-                       Config(cuda_graphs=False, forward_into_copies=False, write_through_copies=False,
-                              graph_streams=1), dev)
+                       Config(cuda_graphs=False).as_scheduled(), dev)
     assert cm.executed_schedule.plan.offsets == shifted.plan.offsets
     arena = cm._get_arena()
     arena.fill_(0xA5)
@@ -164,7 +163,7 @@ def test_forked_graph_stays_equal_to_the_serial_chain_under_changing_inputs(dev)
 
     s = load_schedule("bert-base_b8_s128_float16")
     model, inputs = models.build("bert-base", 8, dtype=torch.float16)
-    serial = CompiledModel(s, model, Config(graph_streams=1, forward_into_copies=False, write_through_copies=False), dev)
+    serial = CompiledModel(s, model, Config().as_scheduled(), dev)
     forked = CompiledModel(s, model, Config(graph_streams=4), dev)
     g = torch.Generator().manual_seed(3)
     for _ in range(40):

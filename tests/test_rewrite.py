@@ -328,3 +328,10 @@ def test_bias_epilogue_and_sequence_first_compose():
     a, _ = oracle.run_schedule(s, model, inputs)
     b, _ = oracle.run_schedule(full, model, inputs)
     assert (a.float() - b.float()).abs().max().item() <= 1e-2
+
+
+def test_as_scheduled_config_switches_every_rewrite_off():
+    for stem in ("bert-base_b4_s128_float16", "gpt2-small_b1_s128_float16"):
+        s = load_schedule(stem)
+        assert rewrite.prepare(s, Config().as_scheduled()) is s
+        assert len(rewrite.prepare(s, Config())) < len(s)
