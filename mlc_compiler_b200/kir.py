@@ -365,8 +365,20 @@ class ExternKernel:
         return [o.buffer for o in self.outputs]
 
     def summary(self) -> str:
-        shapes = "x".join(str(list(v.shape)) for v in self._views())
-        return f"{self.name}: extern {self.op} {shapes}"
+        def show(v: View) -> str:
+            dense, run = [], 1
+            for n in reversed(v.shape):
+                dense.append(run)
+                run *= n
+            text = str(list(v.shape))
+            if tuple(reversed(dense)) != tuple(v.strides) or v.offset:
+                # a strided window: say where it looks
+                text += "@" + str(tuple(v.strides)) + (f"+{v.offset}" if v.offset else "")
+            return text
+        shapes = "x".join(show(v) for v in self._views())
+        outs = [o for o in self.outputs if show(o) != str(list(o.shape))]
+        tail = " -> " + ", ".join(show(o) for o in outs) if outs else ""
+        return f"{self.name}: extern {self.op} {shapes}{tail}"
 
 
 Kernel = PointwiseKernel | ReductionKernel | ExternKernel
