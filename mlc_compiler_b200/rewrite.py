@@ -737,7 +737,7 @@ def _movable(schedule, buffer: str, finals) -> bool:
     return buffer not in finals and schedule.buffers[buffer].plannable
 
 
-def output_major(k: kir.PointwiseKernel) -> kir.PointwiseKernel:
+def output_major(k: kir.PointwiseKernel, order=None) -> kir.PointwiseKernel:
     """``k`` iterating in the order its first output is stored.
 
     A pointwise kernel may visit its elements in any order.  The frontend numbers
@@ -747,7 +747,9 @@ def output_major(k: kir.PointwiseKernel) -> kir.PointwiseKernel:
     access.  The iteration index is cut at every boundary any operand's map uses,
     the resulting digits are re-ordered by the output's stride, and every map is
     rewritten for the new numbering (adjacent digits an operand walks densely are
-    fused again)."""
+    fused again).  ``order`` (a permutation of the digits, innermost first, or a
+    function of their count returning one) overrides the choice; tests use it to
+    scramble a kernel."""
     operands = list(k.inputs) + list(k.outputs)
     if not k.outputs or any(len(a.index.axes) != 1 or a.via is not None for a in operands):
         return k
@@ -772,11 +774,14 @@ def output_major(k: kir.PointwiseKernel) -> kir.PointwiseKernel:
             out.append(st)
         return out
 
-    key = strides(k.outputs[0])
-    if any(st == 0 for st in key):
-        return k
-    order = sorted(range(len(digits)), key=lambda j: key[j])                # innermost first
-    if order == list(range(len(digits))):
+    if order is None:
+        key = strides(k.outputs[0])
+        if any(st == 0 for st in key):
+            return k
+        order = sorted(range(len(digits)), key=lambda j: key[j])            # innermost first
+    elif callable(order):
+        order = order(len(digits))
+    if list(order) == list(range(len(digits))):
         return k
     weight, w = {}, 1
     for j in order:

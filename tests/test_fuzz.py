@@ -106,3 +106,112 @@ def test_special_cases_match_the_oracle_on_the_gpu():
         torch.cuda.synchronize()
         for a in k.outputs:
             assert_close(gpu[a.buffer], buffers[a.buffer], a.dtype, f"{k.name}/{a.name}")
+
+
+@pytest.mark.parametrize("seed", SEEDS)
+def test_iteration_order_never_matters_for_random_pointwise_kernels(seed):
+    """``rewrite.output_major`` renumbers a pointwise kernel's iterations.  Every
+    random kernel (strided / broadcast / padded operands) is first scrambled with a
+    random digit order, then put back into output order; all three must write the
+    same bytes, and the restored one must walk its output in storage order."""
+    import random
+
+    from mlc_compiler_b200 import rewrite
+
+    sched, buffers = corpus(seed)
+    rng = random.Random(seed)
+    scrambled = 0
+    for k in sched.kernels:
+        if not isinstance(k, kir.PointwiseKernel):
+            continue
+
+        def shuffle(n):
+            order = list(range(n))
+            rng.shuffle(order)
+            return order
+        mixed = rewrite.output_major(k, order=shuffle)
+        back = rewrite.output_major(mixed)
+        if mixed is k:
+            continue
+        scrambled += 1
+        assert mixed.numel == back.numel == k.numel
+        strides = [t[2] for t in back.outputs[0].index.axes[0].terms]
+        assert strides == sorted(strides, reverse=True)
+        results = []
+        for variant in (k, mixed, back):
+            bufs = {n: t.clone() for n, t in buffers.items()
+                    if n in set(k.reads()) | set(k.writes())}
+            oracle.run_kernel(variant, bufs)
+            results.append(bufs)
+        # exactly the same (operand offsets..., output offsets...) tuples, in another order
+        def visits(v):
+            ops = list(v.inputs) + list(v.outputs)
+            return sorted(tuple(a.index.offset(idx=i) for a in ops) for i in range(v.numel))
+        if k.numel <= 4096:
+            assert visits(k) == visits(mixed) == visits(back), k.name
+        # and the same values: exact for integers; for floats up to the last bit, because
+        # ATen's CPU kernels round exp/tanh/pow differently in their vector body and their
+        # scalar tail, and renumbering moves elements between the two
+        for out in k.outputs:
+            x = results[0][out.buffer]
+            for other in results[1:]:
+                y = other[out.buffer]
+                if not x.is_floating_point():
+                    assert torch.equal(x, y), k.name
+                    continue
+                x64, y64 = x.double(), y.double()
+                assert torch.equal(torch.isnan(x64), torch.isnan(y64)), k.name
+                torch.testing.assert_close(torch.nan_to_num(y64), torch.nan_to_num(x64),
+                                           rtol=2e-6 if x.dtype == torch.float32 else 1e-2, atol=1e-7)
+        generate_module(kir.Schedule("one", [mixed, kir.PointwiseKernel(
+            back.name + "_b", back.space, back.inputs, back.outputs, back.body, back.out_expr,
+            back.ops)], sched.buffers), Config())
+    assert scrambled >= 10
+
+
+@pytest.mark.gpu
+def test_scrambled_pointwise_kernels_match_the_oracle_on_the_gpu():
+    """The emitter on kernels whose iteration order follows no operand (what a
+    layout rewrite can leave behind) and on the same kernels put back in output
+    order."""
+    import random
+
+    from mlc_compiler_b200 import rewrite
+    from mlc_compiler_b200.runtime import CudaRuntime
+
+    dev = torch.device("cuda", 0)
+    sched, buffers = corpus(SEEDS[0])
+    rng = random.Random(5)
+    kernels = []
+    for k in sched.kernels:
+        if not isinstance(k, kir.PointwiseKernel):
+            continue
+
+        def shuffle(n):
+            order = list(range(n))
+            rng.shuffle(order)
+            return order
+        mixed = rewrite.output_major(k, order=shuffle)
+        if mixed is k:
+            continue
+        back = rewrite.output_major(mixed)
+        kernels.append(kir.PointwiseKernel(k.name + "_m", mixed.space, mixed.inputs, mixed.outputs,
+                                           mixed.body, mixed.out_expr, mixed.ops))
+        kernels.append(kir.PointwiseKernel(k.name + "_b", back.space, back.inputs, back.outputs,
+                                           back.body, back.out_expr, back.ops))
+    assert len(kernels) >= 20
+    rt = CudaRuntime(kir.Schedule("scrambled", kernels, sched.buffers), Config(), dev)
+    failures = []
+    for k in kernels:
+        gpu = {b: buffers[b].to(dev) for b in set(k.reads()) | set(k.writes())}
+        for b in k.writes():
+            gpu[b].fill_(float("nan")) if gpu[b].is_floating_point() else gpu[b].fill_(1)
+        rt.launch(k, gpu)
+        oracle.run_kernel(k, buffers)
+        torch.cuda.synchronize()
+        for a in k.outputs:
+            try:
+                assert_close(gpu[a.buffer], buffers[a.buffer], a.dtype, f"{k.name}/{a.name}")
+            except AssertionError as e:
+                failures.append(str(e))
+    assert not failures, "\n".join(failures[:10])
