@@ -21,6 +21,9 @@ One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line
 * ``replica_throughput``: batch 32 split over the ranks (32/N per GPU), no
   collectives, sequences per second summed over ranks.
 
+``--section replicas`` prints that split for both models in fp16 and bf16 (sequences
+per second, arena per GPU, launches per forward) and nothing else.
+
 With N > 1 (torchrun) every rank runs an independent replica; there is no
 data-path collective, only a barrier and a max/sum of the timings.
 ``--impl reference`` times the CPU oracle alone on rank 0 (the reference's own
@@ -376,6 +379,27 @@ def run_ours(args) -> int:
                           "generated_us": round(sum(r["us_per_launch"] * r["launches_per_forward"]
                                                     for r in fam), 1), "families": fam}))
         return 0
+    if args.section == "replicas":
+        # batch 32 split 32/N per GPU, both models, fp16 and bf16: sequences per second summed
+        # over the ranks and the arena each GPU holds (each per-GPU batch is its own schedule)
+        per_gpu = 32 // world
+        flush = L2Flush(dev)
+        rows = []
+        for name in ("bert-base", "gpt2-small"):
+            for dt in (torch.float16, torch.bfloat16):
+                rcm, rin, rsched = _compiled(name, per_gpu, dt, dev, **cfg_kw)
+                rdev = [t.to(dev) for t in rin]
+                rms = statistics.mean(time_replays(rcm, rdev, max(5, steps // 4), 3, flush))
+                thr = replicated_throughput(group, per_gpu, rms, dev)
+                rows.append({"model": name, "dtype": str(dt).split(".")[-1], "n_gpus": world,
+                             "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
+                             "ms_per_forward": round(thr["ms_per_forward"], 4),
+                             "arena_mb_per_gpu": round(rsched.arena_bytes / 2 ** 20, 2),
+                             "launches_per_forward": len(rcm.executed_schedule)})
+                del rcm
+        if rank == 0:
+            print(json.dumps({"replicas": rows, "l2": "flushed between steps"}))
+        return 0
     if args.section == "compare":
         # same method as the reference's own harness (mlc/bench/runner.py:84-112):
         # median of 50 event-timed calls of compiled(*inputs) after 20 warm-ups, no flush
@@ -521,7 +545,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--section", default="all", choices=("all", "micro", "model", "families", "compare"),
+    ap.add_argument("--section", default="all", choices=("all", "micro", "model", "families", "compare", "replicas"),
                     help="'micro' prints only the fused-kernel microbenchmark table, "
                          "'model' only the device-timed BERT step (both for profiling)")
     ap.add_argument("--model", default="bert-base")
