@@ -2,7 +2,9 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line.
+One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line,
+kept short; the long per-kernel tables go to ``gpurun_out/bench_details.json``
+when that directory can be written.
 
 * ``value`` / ``ms_per_step``: latency of one graph replay with the inputs already
   in device memory, per-step CUDA events, L2 flushed (a 256 MiB write) between
@@ -11,23 +13,31 @@ One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line
   pinned host inputs are copied in, the graph replayed, the result copied back
   to pinned host memory, host wall clock around each step (device drained at the
   end of every step).
-* ``roofline``: the largest fused-kernel microbenchmark (bias+GELU+residual over
-  [32*128, 3072] fp16), timed live as a CUDA graph of launches over rotating
-  buffer sets totalling more than four times L2; ``fused_kernels`` lists all nine
-  microbenchmark shapes, ``in_model`` the per-family device time inside the BERT
-  step (those run out of L2 and are launch-bound at batch 1).
-* ``cpu_baseline``: the CPU oracle (a port of the reference's torch backend)
-  timed on this host's cores on the same workload.
-* ``replica_throughput``: batch 32 split over the ranks (32/N per GPU), no
-  collectives, sequences per second summed over ranks.
-
-``--section replicas`` prints that split for both models in fp16 and bf16 (sequences
-per second, arena per GPU, launches per forward) and nothing else.
+* ``roofline``: the fused-kernel microbenchmarks (LayerNorm, causal softmax,
+  bias+GELU+residual, fp16), timed live as CUDA graphs of launches over rotating
+  buffer sets totalling more than four times L2.  The object describes the
+  *lowest* of the three batch-32 cells; ``cells`` gives all three and
+  ``fused_kernels`` all nine (batch 1, 8, 32).  ``traffic`` is the DRAM byte
+  count of an ncu capture of the same function (looked up by symbol: a kernel
+  that has changed since the capture reports null).
+* ``cpu_baseline``: the reference's own CPU path (``mlc.compile`` with
+  ``Config(backend="torch")`` on the copy of the reference under
+  ``oracle/_ref``) timed on this host's cores on the same workload; where that
+  copy is absent, the CPU oracle (a port) stands in and ``kind`` says so.
+* ``config.replicas``: BERT-base and GPT-2 small, fp16 and bf16, batch 32 split
+  32/N per GPU as independent replicas.  ``seq_per_s`` = 32 / the slowest rank's
+  mean replay time; ``e2e_seq_per_s`` = 32 / the wall time from a common barrier
+  to the moment every rank holds its output shard in pinned host memory (host
+  shard -> device, replay, device -> host).
+* ``config.same_method``: the reference's stock Triton build and this backend
+  compiled from the same model object through ``mlc.compile`` in this process,
+  timed alternately with the reference's own method (20 warm-ups, median of 50
+  event-timed calls, ``mlc/bench/runner.py:84-104``).  N = 1 only; bench-only --
+  Triton is not part of the product.
 
 With N > 1 (torchrun) every rank runs an independent replica; there is no
-data-path collective, only a barrier and a max/sum of the timings.
-``--impl reference`` times the CPU oracle alone on rank 0 (the reference's own
-GPU path is Triton, which this repository does not carry).
+data-path collective, only barriers and a max of the timings.
+``--impl reference`` times the reference's CPU path alone on rank 0.
 """
 
 from __future__ import annotations
@@ -48,12 +58,16 @@ os.environ.setdefault("MLC_CACHE_DIR", str(ROOT / ".mlc_cache"))
 import torch  # noqa: E402
 
 WORKLOAD = "bert-base fp16 b1 s128, one CUDA graph per forward"
-#: dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture
-#: summarised in profiles/micro_kernels_fp16_ncu_full.md (50,343,680 read +
-#: 1,473,024 written while the kernel ran; the remaining 23.7 MB of output were
-#: still dirty in the 126 MB L2 when it ended and are written back afterwards)
-NCU_TRAFFIC = {"micro-gelu:32": 51816704}
 METRIC = "bert_base_fp16_b1_s128_latency"
+#: what both arms state about the workload (the reference arm prints exactly these)
+STATIC_CONFIG = {"workload": WORKLOAD, "accumulate": "f32", "batch": 1, "seq_len": 128,
+                 "kernels_scheduled": 200}
+
+#: dram__bytes_read.sum + dram__bytes_write.sum per launch, by function symbol,
+#: from `ncu --set full` captures of the batch-32 microbenchmarks.  Written
+#: lines that are still dirty in the 126 MB L2 when the kernel ends are not in
+#: the figure, so it can be below the algorithmic bytes.
+NCU_TRAFFIC: dict[str, int] = {}
 
 
 def _peaks() -> tuple[float, str]:
@@ -245,9 +259,12 @@ def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64,
             torch.cuda.synchronize()
             us = s.elapsed_time(e) * 1e3 / (reps * n_launch)
             gbs = spec.alg_bytes / us / 1e3
-            rows.append({"kernel": name, "batch": b, "alg_bytes": spec.alg_bytes,
+            info = rt.kernel_info(k.name)
+            rows.append({"kernel": name, "batch": b, "symbol": rt.generated.symbol[k.name],
+                         "alg_bytes": spec.alg_bytes,
                          "us_per_launch": round(us, 3), "gbs": round(gbs, 1),
                          "frac": round(gbs / peak_gbs, 4), "grid": spec.grid, "block": spec.block,
+                         "registers": info["registers"],
                          "buffer_sets": sets, "set_bytes": per_set,
                          "launches_per_graph": n_launch,
                          "hbm_resident": bool(sets * per_set >= 4 * l2)})
@@ -295,24 +312,200 @@ def in_model_families(cm, dev_inputs, peak_gbs: float, reps: int = 20) -> list[d
     return out
 
 
-def cpu_oracle_times(steps: int, warmup: int) -> tuple[list[float], int, str]:
-    sys.path.insert(0, str(ROOT / "oracle"))
-    import kir_oracle as oracle
-    from mlc_compiler_b200 import models
-    from mlc_compiler_b200.frontend import load_schedule
+# --------------------------------------------------------------------------
+# the reference's CPU path (and the port that stands in where it is absent)
+# --------------------------------------------------------------------------
 
-    sched = load_schedule("bert-base_b1_s128_float16")
+def _host_threads() -> int:
+    # torchrun pins OMP_NUM_THREADS=1; the baseline is meant to use every host core
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
+    return torch.get_num_threads()
+
+
+def reference_cpu_times(steps: int, warmup: int) -> tuple[list[float], int, str, str]:
+    """``(per-step ms, threads, kind, sample)`` of BERT-base fp16 b1 on the host
+    cores: the reference's torch backend behind ``mlc.compile`` when the copy under
+    ``oracle/_ref`` is there (kind "reference"), else the CPU oracle (kind "port")."""
+    from mlc_compiler_b200 import models
+
+    sys.path.insert(0, str(ROOT / "oracle"))
+    cores = _host_threads()
     model, inputs = models.build("bert-base", 1, dtype=torch.float16)
-    table = dict(model.named_parameters(remove_duplicate=False))
-    table.update(dict(model.named_buffers(remove_duplicate=False)))
-    buffers = oracle.allocate(sched, table, inputs)
+    try:
+        import ref as reference_copy
+        reference_copy.activate()
+        import mlc
+        from mlc.config import Config as RefConfig
+    except ImportError:
+        mlc = None
+    if mlc is not None:
+        compiled = mlc.compile(model, inputs, RefConfig(backend="torch", cuda_graphs=False),
+                               device="cpu")
+        run = lambda: compiled(*inputs)                                   # noqa: E731
+        kind = "reference"
+        sample = ("whole forwards of mlc.compile(..., Config(backend='torch', cuda_graphs=False), "
+                  "device='cpu'), perf_counter per call")
+    else:
+        import kir_oracle as oracle
+        from mlc_compiler_b200.frontend import load_schedule
+
+        sched = load_schedule("bert-base_b1_s128_float16")
+        table = dict(model.named_parameters(remove_duplicate=False))
+        table.update(dict(model.named_buffers(remove_duplicate=False)))
+        buffers = oracle.allocate(sched, table, inputs)
+        run = lambda: oracle.run_schedule(sched, table, inputs, buffers=buffers)   # noqa: E731
+        kind = "port"
+        sample = "whole forwards of the same 200-kernel schedule on the CPU oracle"
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        oracle.run_schedule(sched, table, inputs, buffers=buffers)
+        run()
         if i >= warmup:
             times.append((time.perf_counter() - t0) * 1e3)
-    return times, torch.get_num_threads(), "whole forwards of the same 200-kernel schedule"
+    return times, cores, kind, f"{steps} {sample}"
+
+
+def run_reference(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps, warmup = max(1, min(args.steps, 100)), max(0, args.warmup)
+    times, cores, kind, sample = reference_cpu_times(steps, warmup)
+    ms = statistics.mean(times)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(ms, 4), "unit": "ms",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "median_ms": round(statistics.median(times), 4),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": dict(STATIC_CONFIG, device="cpu"),
+        "cpu_baseline": {"value": round(ms, 4), "unit": "ms", "cores": cores, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": round(ms, 4), "unit": "ms", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# --------------------------------------------------------------------------
+# same-method comparison with the reference's Triton build (bench-only)
+# --------------------------------------------------------------------------
+
+def same_method_comparison(dev, rounds: int = 5) -> dict:
+    """Compile one model object three ways through the reference's public
+    ``mlc.compile`` -- its stock Triton backend; this backend under the reference's
+    own executor (``install()``); this backend with this package's executor
+    (``install(native_executor=True)``) -- and time them alternately with the
+    reference's method: 20 warm-up calls, then the median of 50 event-timed calls
+    of ``compiled(*inputs)``, no L2 flush (``mlc/bench/runner.py:84-104``).
+    Returns milliseconds (median over ``rounds`` rounds) per model."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    out: dict = {"method": f"mlc.compile on one model object; 20 warm-ups then median of 50 "
+                           f"event-timed calls, no L2 flush; {rounds} alternating rounds, median"}
+    try:
+        import ref as reference_copy
+        reference_copy.activate()
+        import mlc
+        import triton  # noqa: F401
+        from mlc.config import Config as RefConfig
+    except ImportError as e:
+        out["unavailable"] = f"{type(e).__name__}: {e}"
+        return out
+    import mlc_compiler_b200 as mb
+    from mlc_compiler_b200 import models
+
+    def timed(fn, inputs) -> float:
+        for _ in range(20):
+            fn(*inputs)
+        torch.cuda.synchronize()
+        ts = []
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(50):
+            s.record()
+            fn(*inputs)
+            e.record()
+            e.synchronize()
+            ts.append(s.elapsed_time(e))
+        return statistics.median(ts)
+
+    for name in ("bert-base", "gpt2-small"):
+        key = name.replace("-", "_") + "_b1"
+        try:
+            model, inputs = models.build(name, 1, dtype=torch.float16)
+            model = model.to(dev)
+            inputs = tuple(t.to(dev) for t in inputs)
+            mb.uninstall()
+            arms = {"triton_ref": mlc.compile(model, inputs, RefConfig(), device=dev)}
+            if arms["triton_ref"].backend != "triton":
+                raise RuntimeError(f"reference chose backend {arms['triton_ref'].backend!r}")
+            mb.install()
+            arms["ours_ref_executor"] = mlc.compile(model, inputs, RefConfig(), device=dev)
+            mb.install(native_executor=True)
+            arms["ours"] = mlc.compile(model, inputs, RefConfig(), device=dev)
+            mb.uninstall()
+            want = arms["triton_ref"](*inputs).float()
+            err = {a: float((c(*inputs).float() - want).abs().max()) for a, c in arms.items()}
+            samples = {a: [] for a in arms}
+            for _ in range(rounds):
+                for a, c in arms.items():
+                    samples[a].append(timed(c, inputs))
+            out[key] = {f"{a}_ms": round(statistics.median(v), 4) for a, v in samples.items()}
+            out[key]["max_abs_diff_vs_triton"] = round(max(err.values()), 5)
+            del arms
+        except Exception as e:           # Triton may fail to JIT on a given stack
+            mb.uninstall()
+            out[key] = {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+    return out
+
+
+# --------------------------------------------------------------------------
+# replicas: batch 32 split over the ranks
+# --------------------------------------------------------------------------
+
+def replica_rows(group, dev, steps: int, flush, cfg_kw, combos=None) -> list[dict]:
+    """Batch 32 split 32/N per GPU as independent replicas, for each model and
+    dtype: device-timed replays and the end-to-end variant from pinned host
+    shards to pinned host outputs, both between common barriers."""
+    from mlc_compiler_b200.replicas import shard_inputs, split_throughput
+    from mlc_compiler_b200 import models
+
+    per_gpu = 32 // group.world
+    rows = []
+    for name, dt in combos or [(m, d) for m in ("bert-base", "gpt2-small")
+                               for d in (torch.float16, torch.bfloat16)]:
+        cm, _, sched = _compiled(name, per_gpu, dt, dev, **cfg_kw)
+        # the whole batch of 32 as the host sees it; this rank takes its contiguous share
+        _, full = models.build_inputs(name, 32, dtype=dt)
+        mine = [t.contiguous().pin_memory() for t in shard_inputs(full, group.world, group.rank)]
+        dev_in = [t.to(dev) for t in mine]
+        ms = statistics.mean(time_replays(cm, dev_in, steps, 3, flush))
+        thr = split_throughput(group, 32, ms, dev)
+        out = cm(*mine)
+        host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        e2e = []
+        for i in range(2 + steps):
+            flush()
+            barrier(group)
+            t0 = time.perf_counter()
+            out = cm(*mine)
+            host_out.copy_(out, non_blocking=True)
+            torch.cuda.synchronize()
+            wall = group.max((time.perf_counter() - t0) * 1e3, dev)   # last rank to finish
+            if i >= 2:
+                e2e.append(wall)
+        e2e_ms = statistics.mean(e2e)
+        rows.append({"model": name, "dtype": str(dt).split(".")[-1].replace("float", "f").replace("bf", "bf"),
+                     "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
+                     "ms_slowest": round(thr["ms_per_forward"], 4),
+                     "e2e_seq_per_s": round(32 / (e2e_ms / 1e3), 1), "e2e_ms": round(e2e_ms, 3),
+                     "arena_mb_per_gpu": round(sched.arena_bytes / 2 ** 20, 2),
+                     "launches": len(cm.executed_schedule)})
+        del cm, host_out, out
+    return rows
 
 
 # --------------------------------------------------------------------------
@@ -322,41 +515,26 @@ def barrier(group) -> None:
     torch.cuda.synchronize()
 
 
-def run_reference(args) -> int:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return 0
-    # torchrun pins OMP_NUM_THREADS=1; the baseline is meant to use every host core
+def _write_details(details: dict) -> str | None:
+    out = ROOT / "gpurun_out"
     try:
-        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
-    except (AttributeError, RuntimeError):
-        pass
-    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
-    steps = min(steps, 60)       # ~0.5 s per forward on 8 cores: stays within a few minutes
-    times, cores, sample = cpu_oracle_times(steps, warmup)
-    ms = statistics.mean(times)
-    line = {
-        "impl": "reference", "metric": METRIC, "value": round(ms, 4), "unit": "ms",
-        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
-        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "device": "cpu",
-                                        "accumulate": "f32",
-                                        "note": "reference torch backend restated (oracle port), "
-                                                "all host threads"},
-        "cpu_baseline": {"value": round(ms, 4), "unit": "ms", "cores": cores, "kind": "port",
-                         "sample": f"{steps} {sample}"},
-        "e2e": {"value": round(ms, 4), "unit": "ms", "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line))
-    return 0
+        out.mkdir(exist_ok=True)
+        (out / "bench_details.json").write_text(json.dumps(details, indent=1))
+        return "gpurun_out/bench_details.json"
+    except OSError:
+        return None
+
+
+def _parse_cfg(pairs) -> dict:
+    kw = dict(kv.split("=") for kv in pairs)
+    return {k: (v == "True" if v in ("True", "False") else int(v) if v.lstrip("-").isdigit() else v)
+            for k, v in kw.items()}
 
 
 def run_ours(args) -> int:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the generated kernels have no CPU path")
-    from mlc_compiler_b200.replicas import ReplicaGroup, replicated_throughput
+    from mlc_compiler_b200.replicas import ReplicaGroup
 
     local = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local)
@@ -365,10 +543,8 @@ def run_ours(args) -> int:
     rank, world = group.rank, group.world
     peak, peak_kind = _peaks()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
+    cfg_kw = _parse_cfg(args.cfg)
 
-    cfg_kw = dict(kv.split("=") for kv in args.cfg)
-    cfg_kw = {k: (v == "True" if v in ("True", "False") else int(v) if v.lstrip("-").isdigit() else v)
-              for k, v in cfg_kw.items()}
     if args.section == "families":
         fcm, fin, fs = _compiled(args.model, args.batch, getattr(torch, args.dtype), dev, **cfg_kw)
         fdev = [t.to(dev) for t in fin]
@@ -380,28 +556,16 @@ def run_ours(args) -> int:
                                                     for r in fam), 1), "families": fam}))
         return 0
     if args.section == "replicas":
-        # batch 32 split 32/N per GPU, both models, fp16 and bf16: sequences per second summed
-        # over the ranks and the arena each GPU holds (each per-GPU batch is its own schedule)
-        per_gpu = 32 // world
-        flush = L2Flush(dev)
-        rows = []
-        for name in ("bert-base", "gpt2-small"):
-            for dt in (torch.float16, torch.bfloat16):
-                rcm, rin, rsched = _compiled(name, per_gpu, dt, dev, **cfg_kw)
-                rdev = [t.to(dev) for t in rin]
-                rms = statistics.mean(time_replays(rcm, rdev, max(5, steps // 4), 3, flush))
-                thr = replicated_throughput(group, per_gpu, rms, dev)
-                rows.append({"model": name, "dtype": str(dt).split(".")[-1], "n_gpus": world,
-                             "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
-                             "ms_per_forward": round(thr["ms_per_forward"], 4),
-                             "arena_mb_per_gpu": round(rsched.arena_bytes / 2 ** 20, 2),
-                             "launches_per_forward": len(rcm.executed_schedule)})
-                del rcm
+        rows = replica_rows(group, dev, max(5, steps // 4), L2Flush(dev), cfg_kw)
         if rank == 0:
-            print(json.dumps({"replicas": rows, "l2": "flushed between steps"}))
+            print(json.dumps({"replicas": rows, "n_gpus": world, "l2": "flushed between steps"}))
+        group.close()
+        return 0
+    if args.section == "same-method":
+        print(json.dumps(same_method_comparison(dev)))
         return 0
     if args.section == "compare":
-        # same method as the reference's own harness (mlc/bench/runner.py:84-112):
+        # this backend alone, timed as the reference's harness does (mlc/bench/runner.py:84-112):
         # median of 50 event-timed calls of compiled(*inputs) after 20 warm-ups, no flush
         rows = []
         for name, tag in (("bert-base", ""), ("gpt2-small", ""), ("gpt2-small", "ref")):
@@ -442,6 +606,7 @@ def run_ours(args) -> int:
         rows = micro_roofline(dev, peak, only=args.only, **cfg_kw)
         print(json.dumps({"fused_kernels": rows, "cfg": cfg_kw}))
         return 0
+
     cm, host_inputs, sched = _compiled("bert-base", 1, torch.float16, dev, **cfg_kw)
     dev_inputs = [t.to(dev) for t in host_inputs]
     flush = L2Flush(dev)
@@ -465,75 +630,83 @@ def run_ours(args) -> int:
     e2e_times, h2d, d2h = time_end_to_end(cm, host_inputs, steps, warmup, flush)
     e2e_ms = group.max(statistics.mean(e2e_times), dev)
 
-    # batch 32 split over the ranks, independent replicas
-    per_gpu = 32 // world
-    tcm, tin, tsched = _compiled("bert-base", per_gpu, torch.float16, dev, **cfg_kw)
-    tdev = [t.to(dev) for t in tin]
-    tms = statistics.mean(time_replays(tcm, tdev, max(5, steps // 4), 3, flush))
-    thr = replicated_throughput(group, per_gpu, tms, dev)
-    # and with the per-GPU batch held at 32 (work grows with the replica count)
-    if per_gpu == 32:
-        weak = dict(thr)
-    else:
-        wcm, win, _ = _compiled("bert-base", 32, torch.float16, dev, **cfg_kw)
-        wms = statistics.mean(time_replays(wcm, [t.to(dev) for t in win], max(5, steps // 4), 3, flush))
-        weak = replicated_throughput(group, 32, wms, dev)
-        del wcm
-
-    # BASELINE configuration 3 beside the headline: GPT-2 small fp16 b1, same timing
+    # GPT-2 small fp16 b1 beside the headline, same timing
     gcm, gin, gsched = _compiled("gpt2-small", 1, torch.float16, dev, **cfg_kw)
     gdev = [t.to(dev) for t in gin]
     gpt_ms = group.max(statistics.mean(time_replays(gcm, gdev, max(10, steps // 4), 3, flush)), dev)
     del gcm
 
+    # batch 32 split over the ranks, independent replicas, both models, both narrow dtypes
+    replicas = replica_rows(group, dev, max(5, steps // 4), flush, cfg_kw)
+
+    config = dict(STATIC_CONFIG)
+    config.update({
+        "launched": len(cm.executed_schedule), "generated": cm.generated_launches,
+        "arena_kib": round(sched.arena_bytes / 1024, 1),
+        "l2": "flushed between steps (256 MiB write)",
+        "graph_streams": cm.cfg.graph_streams, "dependent_policy": str(cm.dependent_policy),
+        "parallelism": f"{world} independent replicas, no collectives",
+        "gpt2_small_fp16_b1_ms": round(gpt_ms, 5),
+        "replicas": {"global_batch": 32, "split": f"32/{world} per GPU",
+                     "seq_per_s": "32 / slowest rank's mean replay (device events, L2 flushed)",
+                     "e2e_seq_per_s": "32 / wall time, barrier to every rank's output shard in "
+                                      "pinned host memory",
+                     "rows": replicas},
+    })
     line = {
         "metric": METRIC, "value": round(ms, 5), "unit": "ms", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 5), "median_ms": round(med, 5),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "accumulate": "f32", "kernels": len(sched),
-                   "generated": cm.generated_launches,
-                   "arena_kib": round(sched.arena_bytes / 1024, 1),
-                   "l2": "flushed between steps (256 MiB write)",
-                   "graph_streams": cm.cfg.graph_streams, "dependent_launch": cm.cfg.dependent_launch,
-                   "dependent_policy_chosen": cm.dependent_policy,
-                   "graph_branch_kernels": cm._streams.forked if cm._streams else 0,
-                   "parallelism": f"{world} independent replicas, no collectives"},
+        "data": "synthetic", "config": config,
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
         # generated kernels launched inside the timed region, all ranks together
         "gpu_launches": cm.generated_launches * steps * world,
         "clocks": clocks.summary(),
-        "gpt2_small_fp16_b1_ms": round(gpt_ms, 5),
         "timed_region_wall_s": round(wall, 3),
-        "replica_throughput": {"model": "bert-base fp16 s128", "global_batch": thr["global_batch"],
-                               "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
-                               "ms_per_forward": round(thr["ms_per_forward"], 4),
-                               "arena_mb_per_gpu": round(tsched.arena_bytes / 2**20, 2),
-                               "fixed_per_gpu_batch_32": {
-                                   "global_batch": weak["global_batch"],
-                                   "seq_per_s": round(weak["seq_per_s"], 1),
-                                   "ms_per_forward": round(weak["ms_per_forward"], 4)}},
     }
 
     if rank == 0:
+        details: dict = {"line": line}
         micro = micro_roofline(dev, peak, batches=(1, 8, 32), **cfg_kw)
-        top = max(micro, key=lambda r: r["alg_bytes"])
-        line["roofline"] = {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
-                            "frac": top["frac"],
-                            "traffic": NCU_TRAFFIC.get(f"{top['kernel']}:{top['batch']}"),
-                            "kernel": f"{top['kernel']} b{top['batch']} fp16",
-                            "alg_bytes_per_launch": top["alg_bytes"],
-                            "us_per_launch": top["us_per_launch"], "peak_source": peak_kind}
-        line["fused_kernels"] = micro
-        line["in_model"] = in_model_families(cm, dev_inputs, peak)
+        cells = [r for r in micro if r["batch"] == 32]
+        low = min(cells, key=lambda r: r["frac"])
+        line["roofline"] = {
+            "bound": "hbm", "achieved": low["gbs"], "peak": peak, "unit": "GB/s",
+            "frac": low["frac"], "traffic": NCU_TRAFFIC.get(low["symbol"]),
+            "kernel": f"{low['kernel']} b32 fp16 {low['symbol']} {low['grid']}x{low['block']} "
+                      "(lowest of the three b32 cells)",
+            "alg_bytes_per_launch": low["alg_bytes"], "us_per_launch": low["us_per_launch"],
+            "peak_source": peak_kind,
+            "cells": {f"{r['kernel'][6:]}_b32": {"frac": r["frac"], "us": r["us_per_launch"],
+                                                 "symbol": r["symbol"],
+                                                 "traffic": NCU_TRAFFIC.get(r["symbol"])}
+                      for r in cells}}
+        line["fused_kernels"] = [[r["kernel"][6:], r["batch"], r["us_per_launch"], r["frac"]]
+                                 for r in micro]
+        details["fused_kernels"] = micro
+        details["in_model"] = in_model_families(cm, dev_inputs, peak)
+        gen_us = sum(r["us_per_launch"] * r["launches_per_forward"] for r in details["in_model"])
+        config["generated_us_per_step"] = round(gen_us, 1)
         if world == 1 and not args.no_cpu:
-            times, cores, sample = cpu_oracle_times(10, 1)
+            times, cores, kind, sample = reference_cpu_times(10, 1)
             line["cpu_baseline"] = {"value": round(statistics.mean(times), 3), "unit": "ms",
-                                    "cores": cores, "kind": "port", "sample": f"10 {sample}"}
+                                    "cores": cores, "kind": kind, "sample": sample}
+        if world == 1 and not args.no_triton:
+            sm = same_method_comparison(dev)
+            details["same_method"] = sm
+            bert = sm.get("bert_base_b1", {})
+            gpt = sm.get("gpt2_small_b1", {})
+            config["triton_ref_ms"] = bert.get("triton_ref_ms")
+            config["ours_same_method_ms"] = bert.get("ours_ms")
+            config["same_method"] = {k: v for k, v in sm.items() if k != "method"}
+            if "unavailable" in sm or "unavailable" in bert:
+                config["triton_note"] = sm.get("unavailable") or bert.get("unavailable")
+            del gpt
+        line["details"] = _write_details(details)
     barrier(group)
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line, separators=(",", ":")))
     group.close()
     return 0
 
@@ -545,7 +718,10 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--section", default="all", choices=("all", "micro", "model", "families", "compare", "replicas"),
+    ap.add_argument("--no-triton", action="store_true",
+                    help="skip the same-method comparison with the reference's Triton build")
+    ap.add_argument("--section", default="all",
+                    choices=("all", "micro", "model", "families", "compare", "replicas", "same-method"),
                     help="'micro' prints only the fused-kernel microbenchmark table, "
                          "'model' only the device-timed BERT step (both for profiling)")
     ap.add_argument("--model", default="bert-base")

@@ -48,6 +48,18 @@ class Config:
     reduction_max_packs: int = 8
     #: force the number of threads that share one row (0 = choose)
     reduction_group: int = 0
+    #: force the rows one CTA of a sub-warp row reduction covers (0 = choose)
+    reduction_rows_per_cta: int = 0
+    #: CTAs of a row reduction the compiler must keep resident per SM (caps the
+    #: registers per thread through ``__launch_bounds__``; 0 = 512 threads' worth)
+    reduction_min_ctas: int = 0
+    #: load operands that no kernel of the schedule writes (weights, biases, masks)
+    #: and do all index arithmetic *before* the grid-dependency wait, so that under
+    #: programmatic dependent launch they overlap the predecessor's tail
+    hoist_stable_loads: bool = True
+    #: release the dependent launch right after the wait instead of after the
+    #: kernel's own loads have been issued
+    trigger_early: bool = False
     #: kernels whose every output is fp16/bf16 may use SFU-based exp/tanh/erf and
     #: division (error ~1e-6, below half-precision resolution); fp32 kernels never do
     narrow_fast_math: bool = True

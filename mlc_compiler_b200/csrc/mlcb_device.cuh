@@ -124,6 +124,23 @@ __device__ __forceinline__ void mlcb_load(const T* __restrict__ p,
     for (int i = 0; i < W; ++i) dst[i] = mlcb_elem<T>::get(u.e[i]);
 }
 
+// The same access in two halves: the packed words now (they can sit in a
+// quarter of the registers while other work proceeds -- e.g. weights fetched
+// before the grid-dependency wait), the widening to register type at the use.
+template <typename T, int W>
+__device__ __forceinline__ void mlcb_load_raw(const T* __restrict__ p, mlcb_pack<T, W>& u) {
+    typedef typename mlcb_pack<T, W>::word word;
+    const word* q = reinterpret_cast<const word*>(p);
+#pragma unroll
+    for (int i = 0; i < mlcb_pack<T, W>::N; ++i) u.w[i] = mlcb_ld_word(q + i);
+}
+template <typename T, int W>
+__device__ __forceinline__ void mlcb_unpack(const mlcb_pack<T, W>& u,
+                                            typename mlcb_elem<T>::reg (&dst)[W]) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) dst[i] = mlcb_elem<T>::get(u.e[i]);
+}
+
 // Same, into elements [at, at + W) of a wider register array.
 template <typename T, int W, int V>
 __device__ __forceinline__ void mlcb_load_at(const T* __restrict__ p,

@@ -80,12 +80,15 @@ def _chunks(acc: Access, v: int):
 
 
 def emit_pointwise(k: kir.PointwiseKernel, cfg, buffers: dict[str, kir.BufferSpec] | None = None,
-                   name: str | None = None) -> tuple[str, LaunchSpec]:
+                   name: str | None = None, stable=frozenset()) -> tuple[str, LaunchSpec]:
+    """``stable`` names buffers whose contents are fixed before the first launch
+    (parameters nothing writes); their loads are issued ahead of the
+    grid-dependency wait."""
     with X.math_mode(X.wants_fast_math(k, cfg)):
-        return _emit_pointwise(k, cfg, buffers, name)
+        return _emit_pointwise(k, cfg, buffers, name, stable)
 
 
-def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
+def _emit_pointwise(k, cfg, buffers, name, stable=frozenset()) -> tuple[str, LaunchSpec]:
     name = name or k.name
     numel = k.numel
     operands = list(k.inputs) + list(k.outputs)
@@ -128,7 +131,6 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
              f'{name}({", ".join(params)}) {{')
     L.append(f"    // pointwise {list(k.space)} = {numel} elements, {V} per thread, "
              f"{grid} x {block} threads")
-    L.append("    MLCB_GRID_WAIT();")
     L.append(f"    const {it} pack = ({it})blockIdx.x * {block} + threadIdx.x;")
     if guard:
         L.append(f"    if (pack >= {packs}) return;")
@@ -138,30 +140,46 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
     at_i0 = {"idx": "i0"}
     loads: list[X.Val] = []
     inner: list[str] = []   # per-element loads placed inside the lane loop
+    early: list[str] = []   # loads of stable operands: issued before the wait
+    after: list[str] = []   # everything that may read a predecessor's output
     need_idx = False
     for i, a in enumerate(k.inputs):
         acc = classify(a.index, "idx", V)
         st, rt = X.STORAGE_T[a.dtype], X.REG_T[a.dtype]
         vdt = X.promoted_load_dtype(a.dtype)
+        ahead = a.buffer in stable
         if acc.mode == "bcast" and acc.width == V:
-            L.append(f"    const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, at_i0)}));"
-                     f"  // {a.name}")
+            (early if ahead else after).append(
+                f"    const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, at_i0)}));"
+                f"  // {a.name}")
             loads.append(X.Val(f"v{i}", vdt))
         elif acc.mode == "contig" and acc.width == V and V > 1:
-            L.append(f"    {rt} v{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + ({render_offset(a.index, at_i0)}), v{i});"
-                     f"  // {a.name}")
+            if ahead:
+                # the packed words travel across the wait; widened where the others are
+                early.append(f"    mlcb_pack<{st}, {V}> w{i}; mlcb_load_raw<{st}, {V}>(in{i} + "
+                             f"({render_offset(a.index, at_i0)}), w{i});  // {a.name}")
+                after.append(f"    {rt} v{i}[{V}]; mlcb_unpack<{st}, {V}>(w{i}, v{i});")
+            else:
+                after.append(f"    {rt} v{i}[{V}]; mlcb_load<{st}, {V}>(in{i} + "
+                             f"({render_offset(a.index, at_i0)}), v{i});  // {a.name}")
             loads.append(X.Val(f"v{i}[j]", vdt))
         elif acc.mode == "contig" and acc.width > 1:
-            L.append(f"    {rt} v{i}[{V}];  // {a.name}: runs of {acc.width}")
+            after.append(f"    {rt} v{i}[{V}];  // {a.name}: runs of {acc.width}")
             for c in _chunks(acc, V):
                 off = render_offset(a.index, {"idx": f"(i0 + {c})"})
-                L.append(f"    mlcb_load_at<{st}, {acc.width}, {V}>(in{i} + ({off}), v{i}, {c});")
+                after.append(f"    mlcb_load_at<{st}, {acc.width}, {V}>(in{i} + ({off}), v{i}, {c});")
             loads.append(X.Val(f"v{i}[j]", vdt))
         else:
             need_idx = True
             inner.append(f"        const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, names)}));"
                          f"  // {a.name}")
             loads.append(X.Val(f"v{i}", vdt))
+    L += early
+    L.append("    MLCB_GRID_WAIT();")
+    if getattr(cfg, "trigger_early", False) and dependent_release(grid, block, cfg):
+        L.append(dependent_release(grid, block, cfg))
+    # operands a predecessor may have written first: their latency is the critical path
+    L += [ln for ln in after if "mlcb_unpack" not in ln] + [ln for ln in after if "mlcb_unpack" in ln]
 
     out_acc = []
     for i, a in enumerate(k.outputs):
@@ -174,7 +192,7 @@ def _emit_pointwise(k, cfg, buffers, name) -> tuple[str, LaunchSpec]:
         else:
             need_idx = True
 
-    if dependent_release(grid, block, cfg):
+    if not getattr(cfg, "trigger_early", False) and dependent_release(grid, block, cfg):
         L.append(dependent_release(grid, block, cfg))
     L.append("#pragma unroll")
     L.append(f"    for (int j = 0; j < {V}; ++j) {{")
@@ -343,7 +361,6 @@ def _emit_tiled(k: kir.PointwiseKernel, cfg, name: str, V: int, tile: Tile) -> t
              f'{name}({", ".join(params)}) {{')
     L.append(f"    // transposing pointwise {list(k.space)} = {numel} elements; {V}x{V} register tile per "
              f"thread over digits r=({nr} @ {o_r}) and t=({n0} @ 1); {grid} x {block} threads")
-    L.append("    MLCB_GRID_WAIT();")
     L.append(f"    const {it} micro = ({it})blockIdx.x * {block} + threadIdx.x;")
     if micro % block:
         L.append(f"    if (micro >= {micro}) return;")
@@ -354,6 +371,7 @@ def _emit_tiled(k: kir.PointwiseKernel, cfg, name: str, V: int, tile: Tile) -> t
     L.append(f"    const {it} rest = w / {WT * WR};")
     L.append(f"    const {it} base_idx = t_oct * {V} + (rest % {M}) * {n0} + r_oct * {V * o_r} "
              f"+ (rest / {M}) * {o_r * nr};")
+    L.append("    MLCB_GRID_WAIT();")
 
     loads: list[X.Val | None] = [None] * len(k.inputs)
     for i, a in enumerate(k.inputs):

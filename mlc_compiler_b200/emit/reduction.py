@@ -125,6 +125,9 @@ def plan_geometry(n_rows: int, n_cols: int, operands, cfg, streamed: bool,
         # keep at least two CTAs per SM in flight before packing more rows per CTA
         while rpb > max(1, 32 // G) and (n_rows + rpb - 1) // rpb < 2 * SM_COUNT:
             rpb //= 2
+        want_rows = int(getattr(cfg, "reduction_rows_per_cta", 0) or 0)
+        if want_rows:
+            rpb = max(max(1, 32 // G), min(1024 // G, pow2_ceil(want_rows)))
         block = G * rpb
     grid = (n_rows + rpb - 1) // rpb
     return Geometry(V, P, G, NP, block, rpb, grid, masked=(NP * G != P))
@@ -150,8 +153,10 @@ def varying_steps(k: kir.ReductionKernel) -> set[str]:
 class _Ctx:
     """Bookkeeping for one kernel emission."""
 
-    def __init__(self, k: kir.ReductionKernel, geo: Geometry, it: str):
+    def __init__(self, k: kir.ReductionKernel, geo: Geometry, it: str, stable=frozenset()):
         self.k, self.geo, self.it = k, geo, it
+        #: input slots whose buffer nothing writes: loadable before the wait
+        self.ahead = {i for i, a in enumerate(k.inputs) if a.buffer in stable and a.via is None}
         self.elide = X.store_only_casts([(s.name, s.expr) for s in k.steps if isinstance(s, Bind)],
                                         {n: e for n, e in k.out_expr.items()
                                          if n not in k.row_outputs},
@@ -170,7 +175,7 @@ class _Ctx:
         self.lines.append(s)
 
 
-def _signature(k, name: str, block: int) -> str:
+def _signature(k, name: str, block: int, cfg=None) -> str:
     aliased = {a.buffer for a in k.inputs} & {a.buffer for a in k.outputs}
     params = []
     for i, a in enumerate(k.inputs):
@@ -182,13 +187,13 @@ def _signature(k, name: str, block: int) -> str:
     # the second bound keeps at least 512 threads resident per SM, which caps the
     # allocation at 128 registers per thread; without it ptxas aims far lower and
     # serialises the row's loads (or spills)
-    return (f'extern "C" __global__ void __launch_bounds__({block}, {max(1, min(16, 512 // block))}) '
+    resident = int(getattr(cfg, "reduction_min_ctas", 0) or 0) or max(1, min(16, 512 // block))
+    return (f'extern "C" __global__ void __launch_bounds__({block}, {resident}) '
             f'{name}({", ".join(params)}) {{')
 
 
 def _row_setup(c: _Ctx, n_rows: int, n_red: int) -> None:
     g, it = c.geo, c.it
-    c.emit("    MLCB_GRID_WAIT();")
     if g.cta_row:
         c.emit(f"    const int lane = threadIdx.x;")
         c.emit(f"    const {it} row = blockIdx.x;")
@@ -205,18 +210,19 @@ def _row_setup(c: _Ctx, n_rows: int, n_red: int) -> None:
             c.emit("    const bool live = true;")
 
 
-def _scalar_loads(c: _Ctx) -> list[X.Val | None]:
+def _scalar_loads(c: _Ctx, ahead: bool, out: list | None = None) -> list[X.Val | None]:
     """Operands indexed by row alone: one scalar load per row
-    (``triton_reduction.py:103-110``)."""
-    out: list[X.Val | None] = []
+    (``triton_reduction.py:103-110``).  Called twice: for the operands that may be
+    read before the grid-dependency wait (``ahead``), then for the rest."""
+    if out is None:
+        out = [None] * len(c.k.inputs)
     for i, a in enumerate(c.k.inputs):
-        if a.index.varies_along("col"):
-            out.append(None)
+        if a.index.varies_along("col") or (i in c.ahead) != ahead:
             continue
         st, rt = X.STORAGE_T[a.dtype], X.REG_T[a.dtype]
         off = render_offset(a.index, {"row": "row"}, skip=("col",))
         c.emit(f"    const {rt} s{i} = mlcb_load1<{st}>(in{i} + ({off}));  // {a.name} (per row)")
-        out.append(X.Val(f"s{i}", X.promoted_load_dtype(a.dtype), True, False))
+        out[i] = X.Val(f"s{i}", X.promoted_load_dtype(a.dtype), True, False)
     return out
 
 
@@ -235,9 +241,13 @@ def _finish_reduce(c: _Ctx, r: Reduce, acc_dt: str, rdt: str, ordinal: int) -> N
     c.scalars[r.name] = X.Val(r.name, rdt, True, False)
 
 
-def _row_offsets(c: _Ctx, operands, prefix: str) -> None:
+def _row_offsets(c: _Ctx, operands, prefix: str, ahead: bool | None = None) -> None:
+    """``ahead`` selects the inputs loadable before the wait (True), the others
+    (False) or all (None); output offsets are plain arithmetic and go first."""
     for i, a in enumerate(operands):
         if prefix == "in" and not a.index.varies_along("col"):
+            continue
+        if prefix == "in" and ahead is not None and (i in c.ahead) != ahead:
             continue
         if prefix == "out" and a.name in c.k.row_outputs:
             continue                               # stored once per row, at its own offset
@@ -261,7 +271,7 @@ def _col_off(a, var: str) -> str:
 # persistent form
 # --------------------------------------------------------------------------
 
-def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchSpec]:
+def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset()) -> tuple[str, LaunchSpec]:
     operands = [a for a in k.inputs if a.index.varies_along("col")] + [
         a for a in k.outputs if a.name not in k.row_outputs]
     geo = plan_geometry(k.n_rows, k.n_cols, operands or k.inputs + k.outputs, cfg, False,
@@ -270,17 +280,23 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
     extents = [k.n_rows * max(1, k.n_cols)] + [a.index.bounds()[1] + 1
                                                for a in k.inputs + k.outputs]
     it = "i64" if needs_64bit(*extents) else "int"
-    c = _Ctx(k, geo, it)
+    c = _Ctx(k, geo, it, stable)
     reduces = k.reduces
     n_phases = len(reduces) + 1
 
-    c.emit(_signature(k, name, geo.block))
+    c.emit(_signature(k, name, geo.block, cfg))
     c.emit(f"    // persistent: {k.n_rows} rows x {k.n_cols} cols; {G} lanes per row, "
            f"{NP} packs of {V} per lane, {geo.rpb} rows per CTA, grid {geo.grid}")
     _row_setup(c, k.n_rows, len(reduces))
-    scalar_in = _scalar_loads(c)
-    _row_offsets(c, k.inputs, "in")
     _row_offsets(c, k.outputs, "out")
+    _row_offsets(c, k.inputs, "in", ahead=True)
+    scalar_in = _scalar_loads(c, True)
+    mark_ahead = len(c.lines)      # packed loads of stable operands are spliced in here
+    c.emit("    MLCB_GRID_WAIT();")
+    if getattr(cfg, "trigger_early", False) and dependent_release(geo.grid, geo.block, cfg):
+        c.emit(dependent_release(geo.grid, geo.block, cfg))
+    _scalar_loads(c, False, scalar_in)
+    _row_offsets(c, k.inputs, "in", ahead=False)
 
     # ---- which phase defines / uses each column-varying value -------------
     phase_of: dict[str, int] = {}
@@ -320,6 +336,25 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
             acc_out[i] = ac if ac.mode == "contig" else Access("contig", 1)
 
     packed_in = {i for i, ac in acc_in.items() if ac.width > 1}
+    # stable operands read as whole packs: fetched before the wait as packed words
+    # (a quarter of the registers of the widened form), widened where first used
+    raw_in = sorted(i for i in packed_in if i in c.ahead and i in load_first
+                    and acc_in[i].mode == "contig" and acc_in[i].width == V)
+    if raw_in:
+        pre = []
+        for i in raw_in:
+            pre.append(f"    mlcb_pack<{X.STORAGE_T[k.inputs[i].dtype]}, {V}> w{i}[{NP}];"
+                       f"  // {k.inputs[i].name}: read ahead of the wait")
+        pre.append("#pragma unroll")
+        pre.append(f"    for (int q = 0; q < {NP}; ++q) {{")
+        pre.append(f"        const int c0 = (lane + q * {G}) * {V};")
+        guard = f"if (c0 < {k.n_cols}) " if geo.masked else ""
+        for i in raw_in:
+            a = k.inputs[i]
+            pre.append(f"        {guard}mlcb_load_raw<{X.STORAGE_T[a.dtype]}, {V}>(in{i} + in{i}_r + "
+                       f"({_col_off(a, 'c0')}), w{i}[q]);")
+        pre.append("    }")
+        c.lines[mark_ahead:mark_ahead] = pre
     for i in sorted(packed_in):
         if i in load_first:
             c.emit(f"    {X.REG_T[k.inputs[i].dtype]} v{i}[{NP}][{V}];  // {k.inputs[i].name}")
@@ -416,6 +451,8 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
                 for r_, cc in enumerate(range(0, V, ac.width)):
                     c.emit(f"{ind}v{i}[q][{r_}] = mlcb_load1<{st}>(in{i} + in{i}_r + "
                            f"({_col_off(a, f'(c0 + {cc})')}));")
+            elif i in raw_in:
+                c.emit(f"{ind}mlcb_unpack<{st}, {V}>(w{i}[q], v{i}[q]);")
             elif ac.width == V:
                 c.emit(f"{ind}mlcb_load<{st}, {V}>(in{i} + in{i}_r + ({_col_off(a, 'c0')}), v{i}[q]);")
             else:
@@ -472,7 +509,8 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, Launc
         c.emit("    }")
         if red is not None:
             _finish_reduce(c, red, acc_dt, rdt, reduces.index(red))
-        if ph == 0 and dependent_release(geo.grid, geo.block, cfg):
+        if ph == 0 and not getattr(cfg, "trigger_early", False) \
+                and dependent_release(geo.grid, geo.block, cfg):
             c.emit(dependent_release(geo.grid, geo.block, cfg))
 
     _row_stores(c, loads)
@@ -592,7 +630,7 @@ def plan_passes(k: kir.ReductionKernel) -> list[Pass]:
     return passes
 
 
-def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchSpec]:
+def _emit_streamed(k: kir.ReductionKernel, cfg, name: str, stable=frozenset()) -> tuple[str, LaunchSpec]:
     operands = [a for a in k.inputs if a.index.varies_along("col")] + [
         a for a in k.outputs if a.name not in k.row_outputs]
     geo = plan_geometry(k.n_rows, k.n_cols, operands or k.inputs + k.outputs, cfg, True)
@@ -600,18 +638,21 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
     extents = [k.n_rows * max(1, k.n_cols)] + [a.index.bounds()[1] + 1
                                                for a in k.inputs + k.outputs]
     it = "i64" if needs_64bit(*extents) else "int"
-    c = _Ctx(k, geo, it)
+    c = _Ctx(k, geo, it, stable)
     passes = plan_passes(k)
     reduces = k.reduces
     by_reduce = {r.name: p for p in passes for r in p.reduces}
 
-    c.emit(_signature(k, name, geo.block))
+    c.emit(_signature(k, name, geo.block, cfg))
     c.emit(f"    // streamed: {k.n_rows} rows x {k.n_cols} cols, {len(passes)} passes over the row; "
            f"{G} lanes per row, packs of {V}, {geo.rpb} rows per CTA, grid {geo.grid}")
     _row_setup(c, k.n_rows, len(reduces) + 1)
-    scalar_in = _scalar_loads(c)
-    _row_offsets(c, k.inputs, "in")
     _row_offsets(c, k.outputs, "out")
+    _row_offsets(c, k.inputs, "in", ahead=True)
+    scalar_in = _scalar_loads(c, True)
+    c.emit("    MLCB_GRID_WAIT();")
+    _scalar_loads(c, False, scalar_in)
+    _row_offsets(c, k.inputs, "in", ahead=False)
     if dependent_release(geo.grid, geo.block, cfg):
         c.emit(dependent_release(geo.grid, geo.block, cfg))
 
@@ -803,7 +844,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str) -> tuple[str, LaunchS
 
 
 def emit_reduction(k: kir.ReductionKernel, cfg, buffers: dict[str, kir.BufferSpec] | None = None,
-                   name: str | None = None) -> tuple[str, LaunchSpec]:
+                   name: str | None = None, stable=frozenset()) -> tuple[str, LaunchSpec]:
     if buffers is not None:
         for a in list(k.inputs) + list(k.outputs):
             check_bounds(a.index, buffers[a.buffer].numel, f"{k.name}:{a.name}")
@@ -820,4 +861,5 @@ def emit_reduction(k: kir.ReductionKernel, cfg, buffers: dict[str, kir.BufferSpe
         raise ValueError(f"{k.name}: outputs cannot be gathered")
     name = name or k.name
     with X.math_mode(X.wants_fast_math(k, cfg)):
-        return _emit_streamed(k, cfg, name) if k.two_pass else _emit_persistent(k, cfg, name)
+        return (_emit_streamed(k, cfg, name, stable) if k.two_pass
+                else _emit_persistent(k, cfg, name, stable))

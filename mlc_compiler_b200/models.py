@@ -284,6 +284,24 @@ def build(name: str, batch: int = 1, seq: int = 128, dtype: torch.dtype = torch.
     return _cast(model, args, dtype)
 
 
+def build_inputs(name: str, batch: int, seq: int = 128, dtype: torch.dtype = torch.float32,
+                 seed: int = 0):
+    """The seeded example inputs of ``build(name, batch, ...)`` without building the
+    model (same generator, same draws) -- e.g. the whole batch that replicas split.
+    Returns ``(None, inputs)`` so that it unpacks like :func:`build`."""
+    g = torch.Generator().manual_seed(seed + 1)
+    if name == "bert-base":
+        args = (torch.randint(0, EncoderDims().vocab, (batch, seq), generator=g),
+                torch.ones(batch, seq))
+    elif name == "gpt2-small":
+        args = (torch.randint(0, DecoderDims().vocab, (batch, seq), generator=g),)
+    else:
+        raise KeyError(f"no input recipe for {name!r}")
+    if dtype != torch.float32:
+        args = tuple(a.to(dtype) if a.is_floating_point() else a for a in args)
+    return None, args
+
+
 def schedule_name(name: str, batch: int, dtype: torch.dtype, seq: int = 128, tag: str = "") -> str:
     dt = str(dtype).replace("torch.", "")
     return f"{name}{('-' + tag) if tag else ''}_b{batch}_s{seq}_{dt}"

@@ -115,14 +115,18 @@ class ReplicaGroup:
                 dist.destroy_process_group()
 
 
-def replicated_throughput(group: ReplicaGroup, per_rank_batch: int, ms_per_forward: float,
-                          device=None) -> dict:
-    """Whole-job figures from per-rank timings: sequences/s summed over ranks,
-    latency as the slowest rank."""
-    seqs = group.sum(per_rank_batch / (ms_per_forward / 1e3), device)
+def split_throughput(group: ReplicaGroup, global_batch: int, ms_per_forward: float,
+                     device=None) -> dict:
+    """Whole-job figures for one batch split over the replicas: the batch is done
+    when the slowest rank is, so sequences/s = global batch / the slowest rank's
+    time (not the sum of each rank's own rate, which would credit fast ranks for
+    time they spend waiting)."""
+    if global_batch % group.world:
+        raise ValueError(f"global batch {global_batch} does not split evenly over "
+                         f"{group.world} replicas")
     slow = group.max(ms_per_forward, device)
-    return {"global_batch": per_rank_batch * group.world, "per_gpu_batch": per_rank_batch,
-            "seq_per_s": seqs, "ms_per_forward": slow}
+    return {"global_batch": global_batch, "per_gpu_batch": global_batch // group.world,
+            "seq_per_s": global_batch / (slow / 1e3), "ms_per_forward": slow}
 
 
 def run_replica(group: ReplicaGroup, inputs: Sequence[torch.Tensor],

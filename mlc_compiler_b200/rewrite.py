@@ -261,9 +261,11 @@ def _pure_copy(k) -> bool:
     if not isinstance(k, kir.PointwiseKernel) or len(k.inputs) != 1 or len(k.outputs) != 1:
         return False
     e = k.out_expr[k.outputs[0].name]
-    while isinstance(e, Cast) and e.dtype in (k.inputs[0].dtype, "float32") \
-            and k.inputs[0].dtype in kir.FLOAT_DTYPES:
-        e = e.x                                  # widening and back is the identity
+    # widening and back is the identity; float64 -> float32 -> float64 is not
+    while isinstance(e, Cast) and k.inputs[0].dtype in kir.FLOAT_DTYPES and (
+            e.dtype == k.inputs[0].dtype
+            or (e.dtype == "float32" and k.inputs[0].dtype in ("float16", "bfloat16", "float32"))):
+        e = e.x
     return (not k.body and isinstance(e, Load) and k.inputs[0].dtype == k.outputs[0].dtype
             and k.inputs[0].buffer != k.outputs[0].buffer)
 
@@ -728,6 +730,22 @@ def fold_embeddings(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule
 _ROWWISE = {"aten.mm.default": 0, "aten.addmm.default": 1}      # op -> position of the row operand
 
 
+def _rows_independent(k) -> bool:
+    """A matmul whose result row ``i`` depends on row ``i`` of its row operand and
+    on nothing else that varies with ``i``: ``mm``, and ``addmm`` whose ``self`` is
+    the same for every row (a bias vector, a ``[1, F]`` row, a stride-0 broadcast).
+    Only then may the rows of operand and result be permuted together;
+    ``addmm(residual[R, F], x, w)`` adds a different row of ``self`` to every result
+    row and must keep its order."""
+    if not (isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1):
+        return False
+    if k.op == "aten.addmm.default":
+        bias = k.args[0]
+        if isinstance(bias, kir.View):
+            return len(bias.shape) < 2 or bias.shape[0] == 1 or bias.strides[0] == 0
+    return True
+
+
 def _whole_dense(schedule, v) -> bool:
     return (isinstance(v, kir.View) and v.offset == 0 and v.strides == _dense_strides(v.shape)
             and v.numel == schedule.buffers[v.buffer].numel)
@@ -838,7 +856,7 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
     # anchor: bmm -> pure copy -> row operand of a matmul
     anchor = None
     for k in kernels:
-        if not (isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1):
+        if not _rows_independent(k):
             continue
         a = k.args[_ROWWISE[k.op]]
         if not (_whole_dense(schedule, a) and len(a.shape) == 2):
@@ -908,7 +926,7 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
             continue
         if not isinstance(made[0], kir.ExternKernel):
             propose(x, L.dense_digits((B, T, J, H, Dh), (1, 0, 3, 2, 4)))
-        elif J == 1 and made[0].op in _ROWWISE and len(made[0].outputs) == 1:
+        elif J == 1 and _rows_independent(made[0]):
             # written by a matmul itself (bias folded into it): a library call cannot
             # interleave columns, but its rows can come in (t, b) order if its row
             # operand does
@@ -920,7 +938,7 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
                 propose(a.buffer, L.dense_digits((B, T, a.shape[1]), (1, 0, 2)))
     # matmuls fed by a copy of a moved bmm result: row operand and result move together
     for k in kernels:
-        if isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1:
+        if _rows_independent(k):
             a, out = k.args[_ROWWISE[k.op]], k.outputs[0]
             if not (_whole_dense(schedule, a) and _whole_dense(schedule, out) and len(a.shape) == 2
                     and a.shape[0] == B * T and out.shape[0] == B * T):
@@ -932,7 +950,7 @@ def sequence_first(schedule: kir.Schedule, replan: bool = True) -> kir.Schedule:
     tables = {b: d for b, d in tables.items() if d}
 
     def rowwise_pair(k):
-        if isinstance(k, kir.ExternKernel) and k.op in _ROWWISE and len(k.outputs) == 1:
+        if _rows_independent(k):
             return k.args[_ROWWISE[k.op]], k.outputs[0]
         return None
 

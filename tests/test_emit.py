@@ -65,10 +65,56 @@ def test_bias_add_is_fully_packed():
     s = load_schedule("bert-base_b1_s128_float16")
     k = s.kernel("k7")
     text = generate_module(s, Config()).kernel_source("k7")
-    assert text.count("mlcb_load<__half, 8>") == 2
+    # the matmul result is read after the wait, the bias (a parameter) ahead of it
+    assert text.count("mlcb_load<__half, 8>") == 1 and text.count("mlcb_load_raw<__half, 8>") == 1
     assert "mlcb_store<__half, 8>" in text
     assert "if (pack >=" not in text
     assert classify(k.inputs[1].index, "idx", 8).width == 8
+    plain = generate_module(s, Config(hoist_stable_loads=False)).kernel_source("k7")
+    assert plain.count("mlcb_load<__half, 8>") == 2 and "mlcb_load_raw" not in plain
+
+
+def _before_and_after_the_wait(text: str) -> tuple[str, str]:
+    head, _, tail = text.partition("MLCB_GRID_WAIT();")
+    assert tail, "kernel has no grid-dependency wait"
+    return head, tail
+
+
+def test_only_parameters_nothing_writes_are_read_ahead_of_the_wait():
+    """Under programmatic dependent launch a kernel may run ahead of its
+    predecessor up to the wait: weights, biases and masks are loaded there, every
+    operand a kernel of the schedule may have produced after it, and no store ever
+    precedes it."""
+    from mlc_compiler_b200.emit.module import stable_buffers
+
+    for stem in ("bert-base_b1_s128_float16", "gpt2-small_b8_s128_bfloat16",
+                 "micro-layernorm_b32_s128_float16", "micro-softmax_b32_s128_float16",
+                 "micro-gelu_b32_s128_float16", "bert-base-streamed_b1_s128_float16"):
+        s = load_schedule(stem)
+        stable = stable_buffers(s)
+        assert stable <= set(s.params)
+        mod = generate_module(s, Config())
+        hoisted = 0
+        for k in s.generated():
+            head, tail = _before_and_after_the_wait(mod.kernel_source(k.name))
+            assert "mlcb_store" not in head
+            for i, a in enumerate(k.inputs):
+                early = f"in{i} +" in head
+                hoisted += early
+                if early:
+                    assert a.buffer in stable, (stem, k.name, a.name)
+                if a.buffer not in stable:
+                    assert f"in{i} +" not in head and f"in{i} +" in tail
+        assert hoisted >= 1, stem
+
+
+def test_layernorm_weights_cross_the_wait_as_packed_words():
+    s = load_schedule("micro-layernorm_b32_s128_float16")
+    text = generate_module(s, Config()).source
+    head, tail = _before_and_after_the_wait(text[text.index("extern \"C\" __global__"):])
+    assert head.count("mlcb_load_raw<__half, 8>") == 2          # gain and bias
+    assert tail.count("mlcb_unpack<__half, 8>") == 2
+    assert "mlcb_load<__half, 8>(in0" in tail                    # the activations wait
 
 
 def test_head_merge_copy_keeps_wide_accesses():

@@ -1,19 +1,20 @@
-"""Drop-in installation into the reference, exercised where a checkout of the
-reference is present (its path in $MLC_REFERENCE, default: a ``reference``
-directory beside this repository); skipped elsewhere.  CPU only: it checks routing and source generation, not
-execution."""
+"""Drop-in installation into the reference, exercised where the reference can be
+imported (the copy ``oracle/ref.py`` installs, else a checkout named by
+$MLC_REFERENCE or lying beside this repository); skipped elsewhere.  CPU only:
+routing and source generation; ``test_gpu_reference.py`` executes the same
+boundary on a GPU."""
 
-import os
 import pathlib
 import sys
 
 import pytest
 import torch
 
-REF = pathlib.Path(os.environ.get(
-    "MLC_REFERENCE", pathlib.Path(__file__).resolve().parent.parent.parent / "reference"))
-pytestmark = pytest.mark.skipif(not (REF / "mlc" / "api.py").exists(),
-                                reason="reference checkout not present")
+sys.path.insert(0, str(pathlib.Path(__file__).resolve().parent.parent / "oracle"))
+import ref as reference_copy  # noqa: E402
+
+REF = reference_copy.path()
+pytestmark = pytest.mark.skipif(REF is None, reason="reference not present")
 
 
 @pytest.fixture()

@@ -335,3 +335,58 @@ def test_as_scheduled_config_switches_every_rewrite_off():
         s = load_schedule(stem)
         assert rewrite.prepare(s, Config().as_scheduled()) is s
         assert len(rewrite.prepare(s, Config())) < len(s)
+
+
+def test_sequence_first_keeps_the_rows_of_an_addmm_with_a_matrix_valued_self():
+    """``addmm(self, x, w)`` treats rows independently only when ``self`` is the same
+    for every row.  With a ``[B*T, F]`` ``self`` (a residual folded into the matmul)
+    row ``i`` of the result takes row ``i`` of ``self``: permuting the rows of ``x``
+    and of the result to ``(t, b)`` order without ``self`` would add the wrong rows.
+    The rewrite must then either leave that matmul's buffers where they are or
+    re-address every operand; the outputs may not change."""
+    s = rewrite.fold_bias_into_matmul(load_schedule(models.schedule_name("bert-base", 4, torch.float16)))
+    model, inputs = models.build("bert-base", 4, dtype=torch.float16)
+    writer = {b: k for k in s.kernels for b in k.writes()}
+    target = None
+    for k in s.kernels:
+        if isinstance(k, kir.ExternKernel) and k.op == "aten.addmm.default":
+            src = writer.get(k.args[1].buffer)
+            if src is not None and rewrite._pure_copy(src):      # fed by the context clone
+                target = k
+                break
+    assert target is not None
+    rows, cols = target.outputs[0].shape
+    assert rows == 4 * 128
+    s.buffers["p_rowwise_self"] = kir.BufferSpec("p_rowwise_self", (rows, cols), "float16", "param")
+    s.params["p_rowwise_self"] = "rowwise_self"
+    i = s.kernels.index(target)
+    s.kernels[i] = kir.ExternKernel(
+        target.name, target.op,
+        [kir.View("rowwise_self", "p_rowwise_self", (rows, cols), (cols, 1), 0)] + list(target.args[1:]),
+        dict(target.kwargs), list(target.outputs))
+    assert not rewrite._rows_independent(s.kernels[i])
+    table = dict(model.named_parameters(remove_duplicate=False))
+    table.update(dict(model.named_buffers(remove_duplicate=False)))
+    g = torch.Generator().manual_seed(3)
+    table["rowwise_self"] = torch.randn(rows, cols, generator=g).to(torch.float16)
+    want, _ = oracle.run_schedule(s, table, inputs)
+    moved = rewrite.read_through_copies(rewrite.sequence_first(s))
+    assert len(moved) < len(s)                                   # the other layers still lose their copies
+    got, _ = oracle.run_schedule(moved, table, inputs)
+    assert torch.equal(got, want)
+    full, _ = oracle.run_schedule(rewrite.prepare(s, Config()), table, inputs)
+    assert torch.equal(full, want)
+
+
+def test_pure_copy_does_not_see_through_a_narrowing_round_trip():
+    n = 16
+    ax = _ax(n, (n, 1, 1))
+
+    def copy(dtype, via):
+        e = kir.Cast(kir.Cast(kir.Load(0), via), dtype)
+        return kir.PointwiseKernel("k", (n,), [kir.Operand("x", "x", dtype, ax)],
+                                   [kir.Operand("y", "y", dtype, ax)], [], {"y": e}, ["_to_copy"])
+
+    assert rewrite._pure_copy(copy("float16", "float32"))        # widening and back: identity
+    assert rewrite._pure_copy(copy("float32", "float32"))
+    assert not rewrite._pure_copy(copy("float64", "float32"))    # rounds to 24 bits on the way
