@@ -197,10 +197,16 @@ def time_end_to_end(cm, host_inputs, steps: int, warmup: int, flush) -> tuple[li
 
 
 def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64,
-                   only: str | None = None, **cfg_kw) -> list[dict]:
+                   only: str | None = None, branches: int = 0, **cfg_kw) -> list[dict]:
     """Each fused-kernel microbenchmark as a CUDA graph of ``launches`` launches
     cycling over buffer sets whose total size exceeds 4x L2, so every launch
-    reads and writes HBM."""
+    reads and writes HBM.  The launches form one chain (each waits for the one
+    before it, as consecutive kernels of a model do): ``us_per_launch`` therefore
+    includes the fixed latency of a dependent launch.  With ``branches`` > 1 the
+    batch-32 rows also report the same launches captured over that many parallel
+    graph branches (``branches_us`` / ``branches_frac``): independent launches
+    overlapping each other's ramp-up and drain, i.e. the rate the kernel streams
+    at once that latency is hidden."""
     from mlc_compiler_b200 import Config, models
     from mlc_compiler_b200.frontend import load_schedule
     from mlc_compiler_b200.runtime import CudaRuntime
@@ -260,7 +266,32 @@ def micro_roofline(dev, peak_gbs: float, batches=(1, 8, 32), launches: int = 64,
             us = s.elapsed_time(e) * 1e3 / (reps * n_launch)
             gbs = spec.alg_bytes / us / 1e3
             info = rt.kernel_info(k.name)
-            rows.append({"kernel": name, "batch": b, "symbol": rt.generated.symbol[k.name],
+            extra = {}
+            if branches > 1 and b == 32 and sets >= branches:
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2):
+                    main = torch.cuda.current_stream()
+                    lanes = [main] + [torch.cuda.Stream(device=dev) for _ in range(branches - 1)]
+                    for ln in lanes[1:]:
+                        ln.wait_stream(main)
+                    for i in range(n_launch):
+                        with torch.cuda.stream(lanes[i % branches]):
+                            bound[i % sets]()
+                    for ln in lanes[1:]:
+                        main.wait_stream(ln)
+                for _ in range(3):
+                    g2.replay()
+                torch.cuda.synchronize()
+                s.record()
+                for _ in range(reps):
+                    g2.replay()
+                e.record()
+                torch.cuda.synchronize()
+                us2 = s.elapsed_time(e) * 1e3 / (reps * n_launch)
+                extra = {"branches": branches, "branches_us": round(us2, 3),
+                         "branches_frac": round(spec.alg_bytes / us2 / 1e3 / peak_gbs, 4)}
+                del g2
+            rows.append({**extra, "kernel": name, "batch": b, "symbol": rt.generated.symbol[k.name],
                          "alg_bytes": spec.alg_bytes,
                          "us_per_launch": round(us, 3), "gbs": round(gbs, 1),
                          "frac": round(gbs / peak_gbs, 4), "grid": spec.grid, "block": spec.block,
@@ -603,7 +634,7 @@ def run_ours(args) -> int:
         print(json.dumps({"compare": rows, "cfg": cfg_kw}))
         return 0
     if args.section == "micro":
-        rows = micro_roofline(dev, peak, only=args.only, **cfg_kw)
+        rows = micro_roofline(dev, peak, only=args.only, branches=args.branches, **cfg_kw)
         print(json.dumps({"fused_kernels": rows, "cfg": cfg_kw}))
         return 0
 
@@ -643,15 +674,15 @@ def run_ours(args) -> int:
     config.update({
         "launched": len(cm.executed_schedule), "generated": cm.generated_launches,
         "arena_kib": round(sched.arena_bytes / 1024, 1),
-        "l2": "flushed between steps (256 MiB write)",
+        "l2": "flushed between steps",
         "graph_streams": cm.cfg.graph_streams, "dependent_policy": str(cm.dependent_policy),
         "parallelism": f"{world} independent replicas, no collectives",
         "gpt2_small_fp16_b1_ms": round(gpt_ms, 5),
-        "replicas": {"global_batch": 32, "split": f"32/{world} per GPU",
-                     "seq_per_s": "32 / slowest rank's mean replay (device events, L2 flushed)",
-                     "e2e_seq_per_s": "32 / wall time, barrier to every rank's output shard in "
-                                      "pinned host memory",
-                     "rows": replicas},
+        "replicas": {"global_batch": 32, "per_gpu_batch": 32 // world,
+                     "cols": ["model", "dtype", "seq_per_s", "e2e_seq_per_s", "arena_mb_per_gpu",
+                              "launches"],
+                     "rows": [[r["model"], r["dtype"], r["seq_per_s"], r["e2e_seq_per_s"],
+                               r["arena_mb_per_gpu"], r["launches"]] for r in replicas]},
     })
     line = {
         "metric": METRIC, "value": round(ms, 5), "unit": "ms", "n_gpus": world, "steps": steps,
@@ -659,7 +690,7 @@ def run_ours(args) -> int:
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": config,
         "e2e": {"value": round(e2e_ms, 5), "unit": "ms", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "timing": "host wall clock, device drained per step"},
+                "d2h_bytes_per_step": d2h, "timing": "host wall clock, drained per step"},
         # generated kernels launched inside the timed region, all ranks together
         "gpu_launches": cm.generated_launches * steps * world,
         "clocks": clocks.summary(),
@@ -667,20 +698,21 @@ def run_ours(args) -> int:
     }
 
     if rank == 0:
-        details: dict = {"line": line}
-        micro = micro_roofline(dev, peak, batches=(1, 8, 32), **cfg_kw)
+        details: dict = {"line": line, "replicas": replicas}
+        micro = micro_roofline(dev, peak, batches=(1, 8, 32), branches=args.branches, **cfg_kw)
         cells = [r for r in micro if r["batch"] == 32]
         low = min(cells, key=lambda r: r["frac"])
         line["roofline"] = {
             "bound": "hbm", "achieved": low["gbs"], "peak": peak, "unit": "GB/s",
             "frac": low["frac"], "traffic": NCU_TRAFFIC.get(low["symbol"]),
-            "kernel": f"{low['kernel']} b32 fp16 {low['symbol']} {low['grid']}x{low['block']} "
-                      "(lowest of the three b32 cells)",
+            "kernel": f"{low['kernel']} b32 fp16 {low['symbol']} {low['grid']}x{low['block']}, "
+                      "lowest b32 cell, chain of dependent launches",
             "alg_bytes_per_launch": low["alg_bytes"], "us_per_launch": low["us_per_launch"],
             "peak_source": peak_kind,
             "cells": {f"{r['kernel'][6:]}_b32": {"frac": r["frac"], "us": r["us_per_launch"],
                                                  "symbol": r["symbol"],
-                                                 "traffic": NCU_TRAFFIC.get(r["symbol"])}
+                                                 "traffic": NCU_TRAFFIC.get(r["symbol"]),
+                                                 "branches4_frac": r.get("branches_frac")}
                       for r in cells}}
         line["fused_kernels"] = [[r["kernel"][6:], r["batch"], r["us_per_launch"], r["frac"]]
                                  for r in micro]
@@ -699,10 +731,13 @@ def run_ours(args) -> int:
             gpt = sm.get("gpt2_small_b1", {})
             config["triton_ref_ms"] = bert.get("triton_ref_ms")
             config["ours_same_method_ms"] = bert.get("ours_ms")
-            config["same_method"] = {k: v for k, v in sm.items() if k != "method"}
-            if "unavailable" in sm or "unavailable" in bert:
-                config["triton_note"] = sm.get("unavailable") or bert.get("unavailable")
-            del gpt
+            config["same_method"] = {
+                "cols": ["triton_ref_ms", "ours_ref_executor_ms", "ours_ms"],
+                "bert_base_b1": [bert.get(c) for c in ("triton_ref_ms", "ours_ref_executor_ms", "ours_ms")],
+                "gpt2_small_b1": [gpt.get(c) for c in ("triton_ref_ms", "ours_ref_executor_ms", "ours_ms")]}
+            note = sm.get("unavailable") or bert.get("unavailable") or gpt.get("unavailable")
+            if note:
+                config["triton_note"] = note
         line["details"] = _write_details(details)
     barrier(group)
     if rank == 0:
@@ -729,6 +764,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="float16")
     ap.add_argument("--only", default=None, metavar="KERNEL:BATCH",
                     help="with --section micro: one row, e.g. micro-gelu:8")
+    ap.add_argument("--branches", type=int, default=4,
+                    help="parallel graph branches of the extra batch-32 microbenchmark figure (0 = skip)")
     ap.add_argument("--cfg", action="append", default=[], metavar="KEY=VALUE",
                     help="override a Config field (e.g. dependent_launch=True)")
     args = ap.parse_args()

@@ -160,6 +160,26 @@ int need_rtc() {
     return 0;
 }
 
+// Makes `want` the calling thread's current context for the guard's lifetime
+// when it is not already (a thread that has not touched the runtime yet, or one
+// whose current device is another GPU), and restores what was there before.
+struct CtxGuard {
+    bool pushed = false;
+    explicit CtxGuard(CUcontext want) {
+        CUcontext cur = nullptr;
+        if (g_drv.CtxGetCurrent(&cur) != CUDA_SUCCESS || cur != want)
+            pushed = g_drv.CtxPushCurrent(want) == CUDA_SUCCESS;
+    }
+    ~CtxGuard() {
+        if (pushed) {
+            CUcontext popped = nullptr;
+            g_drv.CtxPopCurrent(&popped);
+        }
+    }
+    CtxGuard(const CtxGuard&) = delete;
+    CtxGuard& operator=(const CtxGuard&) = delete;
+};
+
 void copy_log(const std::string& s, char* log, size_t cap) {
     if (!log || cap == 0) return;
     size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
@@ -301,6 +321,7 @@ int mlcb_get_kernel(mlcb_module* m, const char* name, mlcb_kernel** out) {
     *out = nullptr;
     if (int e = need_driver()) return e;
     CUfunction fn = nullptr;
+    CtxGuard in_module_context(m->ctx);
     CUresult r = g_drv.ModuleGetFunction(&fn, m->mod, name);
     if (r != CUDA_SUCCESS) {
         char what[256];
@@ -319,6 +340,7 @@ int mlcb_get_kernel(mlcb_module* m, const char* name, mlcb_kernel** out) {
 int mlcb_kernel_info(mlcb_kernel* k, int* regs, int* static_smem, int* max_threads) {
     if (!k) return fail(MLCB_ERR_ARGUMENT, "mlcb_kernel_info: null kernel");
     if (int e = need_driver()) return e;
+    CtxGuard in_module_context(k->owner->ctx);
     CUresult r;
     if (regs && (r = g_drv.FuncGetAttribute(regs, CU_FUNC_ATTRIBUTE_NUM_REGS, k->fn)) != CUDA_SUCCESS)
         return cu_fail(r, "cuFuncGetAttribute(NUM_REGS)");
@@ -346,7 +368,10 @@ static int launch_one(mlcb_kernel* k, uint32_t grid_x, uint32_t block_x, uint32_
     }
     Driver& d = g_drv;
     CUresult r;
-    for (int attempt = 0; attempt < 2; ++attempt) {
+    // the launch happens in the context the module was loaded into, whatever the
+    // calling thread had current; `stream` must belong to that context
+    CtxGuard in_module_context(k->owner->ctx);
+    {
         if (flags & MLCB_LAUNCH_DEPENDENT) {
             CUlaunchAttribute attr;
             memset(&attr, 0, sizeof attr);
@@ -367,11 +392,6 @@ static int launch_one(mlcb_kernel* k, uint32_t grid_x, uint32_t block_x, uint32_
             r = d.LaunchKernel(k->fn, grid_x, 1, 1, block_x, 1, 1, smem_bytes,
                                (CUstream)(uintptr_t)stream, args, nullptr);
         }
-        // a thread that has not touched the runtime yet has no current context
-        if (r == CUDA_ERROR_INVALID_CONTEXT && attempt == 0 &&
-            d.CtxSetCurrent(k->owner->ctx) == CUDA_SUCCESS)
-            continue;
-        break;
     }
     if (r != CUDA_SUCCESS) {
         char what[256];

@@ -175,7 +175,31 @@ class _Ctx:
         self.lines.append(s)
 
 
-def _signature(k, name: str, block: int, cfg=None) -> str:
+def resident_ctas(geo: "Geometry", cfg, row_registers: int = 0) -> int:
+    """CTAs per SM the compiler is told to keep resident (``__launch_bounds__``),
+    i.e. the cap on registers per thread.
+
+    The floor keeps 512 threads per SM (at most 128 registers each); without it
+    ptxas aims far lower and serialises the row's loads, or spills.  On top of
+    that, a launch that *can* be resident all at once should be: when the grid
+    needs ``n`` CTAs per SM for one wave, ``n`` is requested as long as every
+    thread keeps 64 registers or what the row itself occupies
+    (``row_registers``), whichever is more.  LayerNorm over [4096, 768] with its
+    gain and bias held across the wait is the case in point: left alone ptxas
+    takes 80 registers, six CTAs fit an SM and 1024 CTAs need a second, nearly
+    empty wave (4.4 us); told to fit seven it uses 64 and the launch is one wave
+    (3.7 us)."""
+    forced = int(getattr(cfg, "reduction_min_ctas", 0) or 0)
+    if forced:
+        return forced
+    base = max(1, min(16, 512 // geo.block))
+    need = -(-geo.grid // SM_COUNT)
+    budget = max(64, row_registers)
+    cap = min(2048 // geo.block, 65536 // (geo.block * budget))
+    return max(base, min(need, cap))
+
+
+def _signature(k, name: str, block: int, cfg=None, resident: int | None = None) -> str:
     aliased = {a.buffer for a in k.inputs} & {a.buffer for a in k.outputs}
     params = []
     for i, a in enumerate(k.inputs):
@@ -187,7 +211,8 @@ def _signature(k, name: str, block: int, cfg=None) -> str:
     # the second bound keeps at least 512 threads resident per SM, which caps the
     # allocation at 128 registers per thread; without it ptxas aims far lower and
     # serialises the row's loads (or spills)
-    resident = int(getattr(cfg, "reduction_min_ctas", 0) or 0) or max(1, min(16, 512 // block))
+    if resident is None:
+        resident = int(getattr(cfg, "reduction_min_ctas", 0) or 0) or max(1, min(16, 512 // block))
     return (f'extern "C" __global__ void __launch_bounds__({block}, {resident}) '
             f'{name}({", ".join(params)}) {{')
 
@@ -284,7 +309,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
     reduces = k.reduces
     n_phases = len(reduces) + 1
 
-    c.emit(_signature(k, name, geo.block, cfg))
+    c.emit("")      # the signature: written once the row's register footprint is known
     c.emit(f"    // persistent: {k.n_rows} rows x {k.n_cols} cols; {G} lanes per row, "
            f"{NP} packs of {V} per lane, {geo.rpb} rows per CTA, grid {geo.grid}")
     _row_setup(c, k.n_rows, len(reduces))
@@ -355,6 +380,12 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
                        f"({_col_off(a, 'c0')}), w{i}[q]);")
         pre.append("    }")
         c.lines[mark_ahead:mark_ahead] = pre
+    # registers the row itself occupies: the widest operand row in its register type,
+    # the packed words carried across the wait, and working room
+    words = lambda dt: max(1, kir.ITEMSIZE[dt] // 4) if dt not in kir.NARROW_FLOATS else 1   # noqa: E731
+    row_regs = NP * V * max([words(X.promoted_load_dtype(k.inputs[i].dtype)) for i in packed_in] or [1])
+    row_regs += sum(NP * max(1, V * kir.ITEMSIZE[k.inputs[i].dtype] // 4) for i in raw_in) + 16
+    c.lines[0] = _signature(k, name, geo.block, cfg, resident_ctas(geo, cfg, row_regs))
     for i in sorted(packed_in):
         if i in load_first:
             c.emit(f"    {X.REG_T[k.inputs[i].dtype]} v{i}[{NP}][{V}];  // {k.inputs[i].name}")
@@ -575,6 +606,12 @@ def detect_online_softmax(k: kir.ReductionKernel):
     """A max whose only job is to shift the argument of a summed exponential."""
     rs = k.reduces
     if len(rs) != 2 or rs[0].kind != "max" or rs[1].kind != "sum":
+        return None
+    # the fused pass carries its running max and sum in fp32; a float64 row keeps
+    # the two separate passes, which accumulate in float64 like the persistent form
+    if any(a.dtype == "float64" for a in list(k.inputs) + list(k.outputs)) or any(
+            isinstance(e, kir.Cast) and e.dtype == "float64"
+            for s in k.steps for e in kir.walk(s.expr)):
         return None
     by = {s.name: s for s in k.steps}
 

@@ -328,8 +328,12 @@ class CompiledModel:
         buffers = dict(self.params)
         for v, t in zip(sch.inputs, inputs):
             spec = sch.buffers[v.buffer]
-            buffers[v.buffer] = (t.to(self.device, kir.torch_dtype(spec.dtype))
-                                 .contiguous().reshape(-1))
+            flat = t.to(self.device, kir.torch_dtype(spec.dtype)).contiguous().reshape(-1)
+            if flat.data_ptr() % 32:
+                # a legal view that starts mid-allocation: packed accesses were proven
+                # from aligned bases, so it is copied rather than refused
+                flat = flat.clone()
+            buffers[v.buffer] = flat
         for b in sch.buffers.values():
             if b.name not in buffers and not b.plannable and b.name in self._live:
                 buffers[b.name] = self._empty(b)
@@ -356,6 +360,14 @@ class CompiledModel:
         return outs[0] if len(outs) == 1 else tuple(outs)
 
     def __call__(self, *inputs: torch.Tensor):
+        # everything below enqueues on "the current stream": make that the model's
+        # device's, whichever device the caller has current
+        if torch.cuda.current_device() != self.device.index:
+            with torch.cuda.device(self.device):
+                return self._call(inputs)
+        return self._call(inputs)
+
+    def _call(self, inputs):
         if self.cfg.cuda_graphs and self.schedule.plan.mode == "arena":
             return self._call_captured(inputs)
         return self.forward(*inputs)
@@ -437,12 +449,19 @@ class CompiledModel:
         """Replay the captured graph on the inputs already resident."""
         if self._graph_replay is None:
             raise ExecutionError("nothing captured yet: call the model once")
+        if torch.cuda.current_device() != self.device.index:
+            with torch.cuda.device(self.device):
+                self._graph_replay.replay()
+            return
         self._graph_replay.replay()
 
     # -- profiling -----------------------------------------------------------------
     def profile_kernels(self, inputs, iters: int = 20) -> list[tuple]:
         """Per-kernel device time over the bound plan, in place
         (``executor.py:309-352``): (name, summary, milliseconds)."""
+        if torch.cuda.current_device() != self.device.index:
+            with torch.cuda.device(self.device):
+                return self.profile_kernels(inputs, iters)
         buffers = self._resident_buffers(inputs)
         if self._plan is None:
             self._plan = self._build_plan(buffers)

@@ -208,10 +208,12 @@ class BoundLaunch:
     tensors they are re-read."""
 
     __slots__ = ("lib", "kernel", "grid", "block", "smem", "flags", "tensors", "ptrs",
-                 "nptrs", "name")
+                 "nptrs", "name", "device")
 
-    def __init__(self, lib, kernel, name, grid, block, smem, flags, tensors):
+    def __init__(self, lib, kernel, name, grid, block, smem, flags, tensors, device=None):
         self.lib, self.kernel, self.name = lib, kernel, name
+        #: the device the module lives on: launches go to *its* current stream
+        self.device = device
         self.grid, self.block, self.smem, self.flags = int(grid), int(block), int(smem), int(flags)
         self._set(tuple(tensors))
 
@@ -231,7 +233,7 @@ class BoundLaunch:
         if tensors and tensors is not self.tensors and \
                 any(a is not b for a, b in zip(tensors, self.tensors)):
             self._set(tuple(tensors))
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         code = self.lib.mlcb_launch(self.kernel, self.grid, self.block, self.smem, self.ptrs,
                                     self.nptrs, stream, self.flags)
         if code != 0:
@@ -248,11 +250,12 @@ class LaunchRun:
     def __init__(self, lib, bound: list[BoundLaunch]):
         self.lib = lib
         self.bound = bound  # keeps pointer arrays alive
+        self.device = bound[0].device if bound else None
         self.descs = (_LaunchDesc * len(bound))(*[b.desc() for b in bound])
         self.failed = ctypes.c_int(-1)
 
     def __call__(self) -> None:
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         code = self.lib.mlcb_launch_many(self.descs, len(self.bound), stream,
                                          ctypes.byref(self.failed))
         if code != 0:
@@ -277,6 +280,7 @@ class CudaRuntime:
         self.path = write_source(self.source)
         self.launch_table = self.generated.launch_table()
         index = device.index if device.index is not None else torch.cuda.current_device()
+        self.device = torch.device("cuda", index)
         torch.cuda.init()
         with torch.cuda.device(index):
             torch.cuda.current_stream()  # makes sure the primary context exists
@@ -306,7 +310,7 @@ class CudaRuntime:
         if flags is None:
             flags = self.flags
         fn = BoundLaunch(self.lib, self.loaded.kernel(self.generated.symbol[k.name]), k.name,
-                         spec.grid, spec.block, spec.smem, flags, tensors)
+                         spec.grid, spec.block, spec.smem, flags, tensors, self.device)
         return fn, spec.grid, tensors, {}
 
     def launch(self, k, buffers: dict[str, torch.Tensor]) -> None:

@@ -63,3 +63,34 @@ def assert_close(got, want, dtype_name: str, what: str = ""):
     bound = tol + tol * w[fin].abs()
     assert bool((err <= bound).all()), (
         f"{what}: max abs err {err.max().item():.3e} exceeds {tol:g} abs/rel")
+
+
+def as_float64(d: dict) -> dict:
+    """A float32 fixture with every float32 buffer, operand and tensor made float64
+    (index maps are in elements, so nothing else changes).  No golden outputs: the
+    caller compares with the oracle."""
+    import dataclasses
+
+    import torch
+    from mlc_compiler_b200 import kir
+
+    s = d["schedule"]
+
+    def up(dt):
+        return "float64" if dt == "float32" else dt
+
+    def operand(a):
+        return dataclasses.replace(a, dtype=up(a.dtype))
+
+    kernels = []
+    for k in s.kernels:
+        if isinstance(k, kir.ExternKernel):
+            kernels.append(k)
+        else:
+            kernels.append(dataclasses.replace(k, inputs=[operand(a) for a in k.inputs],
+                                               outputs=[operand(a) for a in k.outputs]))
+    buffers = {n: dataclasses.replace(b, dtype=up(b.dtype)) for n, b in s.buffers.items()}
+    wide = dataclasses.replace(s, kernels=kernels, buffers=buffers)
+    cast = lambda t: t.double() if t.dtype == torch.float32 else t          # noqa: E731
+    return {"schedule": wide, "params": {n: cast(t) for n, t in d["params"].items()},
+            "inputs": [cast(t) for t in d["inputs"]]}

@@ -281,3 +281,17 @@ def test_narrow_loads_widen_and_stores_round_back():
     assert arrays and all(l.strip().startswith("float v") for l in arrays)   # registers hold fp32
     stores = [l for l in src.splitlines() if "mlcb_store<" in l]
     assert stores and all("mlcb_store<__half," in l for l in stores)
+
+
+def test_float64_streamed_softmax_keeps_two_float64_passes():
+    """The fused online-softmax pass carries its running max and sum in fp32; a
+    float64 row must not take it (the reference's torch backend and the
+    persistent form both work in float64)."""
+    from conftest import as_float64
+
+    narrow = load_tiny("oddsm1025__streamed__float32")["schedule"]
+    assert "run_m" in generate_module(narrow, Config()).source
+    wide = as_float64(load_tiny("oddsm1025__streamed__float32"))["schedule"]
+    src = generate_module(wide, Config()).source
+    assert "run_m" not in src and "float acc_" not in src
+    assert "double acc_" in src and "exp(" in src

@@ -164,6 +164,26 @@ def test_streamed_softmax_survives_minus_inf_masks(dev):
     assert_close(got, want, "float16", "streamed softmax with -inf")
 
 
+@pytest.mark.parametrize("stem", ["oddsm1025__streamed__float32", "oddsm1000__default__float32",
+                                  "oddln1025__streamed__float32"])
+def test_float64_rows_keep_float64_accuracy(stem, dev):
+    """float64 kernels against the oracle at float64 resolution (1e-12), streamed
+    softmax included: no step of a float64 row may pass through fp32."""
+    from conftest import as_float64
+    from mlc_compiler_b200.executor import CompiledModel
+
+    d = as_float64(load_tiny(stem))
+    want, _ = oracle.run_schedule(d["schedule"], d["params"], d["inputs"])
+    cm = CompiledModel(d["schedule"], d["params"], Config(), dev)
+    got = cm(*[t.to(dev) for t in d["inputs"]])
+    torch.cuda.synchronize()
+    wants = list(want) if isinstance(want, tuple) else [want]
+    gots = list(got) if isinstance(got, tuple) else [got]
+    for g_, w_ in zip(gots, wants):
+        assert g_.dtype == torch.float64
+        assert float((g_.cpu() - w_).abs().max()) <= 1e-12
+
+
 @pytest.mark.parametrize("name,batch,dtype", [("bert-base", 4, "float16"), ("gpt2-small", 4, "float16"),
                                                ("bert-base", 8, "bfloat16")])
 def test_each_distinct_function_of_a_batched_schedule_matches_the_oracle(name, batch, dtype, dev):
