@@ -67,7 +67,11 @@ STATIC_CONFIG = {"workload": WORKLOAD, "accumulate": "f32", "batch": 1, "seq_len
 #: from `ncu --set full` captures of the batch-32 microbenchmarks.  Written
 #: lines that are still dirty in the 126 MB L2 when the kernel ends are not in
 #: the figure, so it can be below the algorithmic bytes.
-NCU_TRAFFIC: dict[str, int] = {}
+NCU_TRAFFIC: dict[str, int] = {
+    "mlcb_red_4357894e362b": 6302720,              # LayerNorm [4096, 768]: 6,302,720 read + 0 written
+    "mlcb_red_7cbf8dea7dc8": 12623872,             # causal softmax [49152, 128]: 12,623,872 + 0
+    "mlcb_pw_ad8b0a2a3110": 50348800 + 1605888,    # bias+GELU+residual [4096, 3072]
+}
 
 
 def _peaks() -> tuple[float, str]:

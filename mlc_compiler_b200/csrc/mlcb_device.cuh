@@ -30,8 +30,10 @@ typedef unsigned long long u64;
 #define MLCB_NAN_D   __longlong_as_double(0x7ff8000000000000LL)
 
 // Programmatic dependent launch: a kernel launched with the stream-serialisation
-// attribute may start while its predecessor drains; it must not touch global
-// memory before the wait.  Without the attribute both are no-ops.
+// attribute may start while its predecessor drains.  Before the wait it may only
+// read memory that no kernel of the schedule writes (weights, biases, masks: the
+// emitter places exactly those loads there) and must store nothing.  Without
+// the attribute both are no-ops.
 #if defined(MLCB_PDL) && MLCB_PDL
 #define MLCB_GRID_WAIT()    asm volatile("griddepcontrol.wait;" ::: "memory")
 #define MLCB_GRID_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")

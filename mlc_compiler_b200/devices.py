@@ -57,8 +57,8 @@ class DeviceProfile:
 
 
 #: B200 (sm_100, 148 SMs, 1965 MHz boost): 148 x 128 lanes x 2 x 1.965 GHz = 74.5 TFLOP/s fp32
-#: nominal.  The entry holds what :func:`calibrate` measured on a B200 of this
-#: pool: 6.2-6.5 TB/s streaming copy, 67 TFLOP/s on the FMA chain, 5.7 us per
+#: nominal.  The entry holds what :func:`calibrate` measures on a B200 (180 GB HBM3e,
+#: 1 kW): 6.2-6.5 TB/s streaming copy, 67 TFLOP/s on the FMA chain, 5.7 us per
 #: eager launch from Python, 0.53 us per node of a captured chain.
 B200 = DeviceProfile(name="NVIDIA B200", bandwidth=6.459e12, fp32_flops=67.2e12,
                      launch_s=5.7e-6, graph_launch_s=0.55e-6)
@@ -72,6 +72,44 @@ def profile_for(device_name: str) -> DeviceProfile | None:
         if tag in key:
             return prof
     return None
+
+
+def config_for(device_name: str, base: Config | None = None) -> Config:
+    """``base`` with the cost-model fields of the named device, as the reference's
+    ``config_for`` (``mlc/devices.py:168-170``); a device without an entry keeps
+    ``base`` unchanged (the reference's A100 defaults)."""
+    prof = profile_for(device_name)
+    return prof.to_config(base) if prof is not None else (base or Config())
+
+
+def register_with_reference() -> bool:
+    """Put the B200 entry at the head of the reference's own device table
+    (``mlc/devices.py:107-134``), so that ``mlc.devices.profile_for`` -- which its
+    bench harness prices fusion with (``mlc/bench/runner.py:158-161``) -- returns
+    Blackwell constants on a B200 instead of the A100 fallback for an unknown
+    device.  Returns False when the reference is not importable."""
+    try:
+        import importlib
+
+        ref = importlib.import_module("mlc.devices")
+    except ImportError:
+        return False
+    unregister_from_reference()
+    ref.TABLE.insert(0, ("B200", ref.DeviceProfile(
+        name=B200.name, bandwidth=B200.bandwidth, fp32_flops=B200.fp32_flops,
+        launch_overhead=B200.launch_s, graph_launch_overhead=B200.graph_launch_s,
+        l2_bytes=126 * 1024 ** 2, total_memory=180 * 1024 ** 3)))
+    return True
+
+
+def unregister_from_reference() -> None:
+    try:
+        import importlib
+
+        ref = importlib.import_module("mlc.devices")
+    except ImportError:
+        return
+    ref.TABLE[:] = [(k, p) for k, p in ref.TABLE if k != "B200"]
 
 
 # --------------------------------------------------------------------------

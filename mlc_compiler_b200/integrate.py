@@ -7,7 +7,9 @@ The reference has no plugin registry: ``CompiledModel.__init__`` imports
 ``mlc.compile(model, example, Config(...))``, ``compiled.schedule``,
 ``compiled.source()`` and the CLI keep working and run generated CUDA instead.
 ``mlc.codegen.triton_backend.generate_module`` is re-pointed too, because
-``python -m mlc source`` calls it directly (``mlc/__main__.py:116-118``).
+``python -m mlc source`` calls it directly (``mlc/__main__.py:116-118``), and the
+B200 entry is added to the reference's device table (``mlc/devices.py:107-134``),
+which otherwise prices an unknown GPU as an A100.
 """
 
 from __future__ import annotations
@@ -68,6 +70,9 @@ def install(native_executor: bool = False) -> None:
     ex.select_backend = _select_backend
     tr.TritonRuntime = CudaRuntime
     tb.generate_module = _source_text
+    from . import devices
+
+    devices.register_with_reference()      # mlc.devices.profile_for knows the B200 from here on
     api.CompiledModel = _native_factory(_saved["CompiledModel"]) if native_executor \
         else _saved["CompiledModel"]
 
@@ -82,6 +87,9 @@ def uninstall() -> None:
     tr.TritonRuntime = _saved["TritonRuntime"]
     tb.generate_module = _saved["generate_module"]
     importlib.import_module("mlc.api").CompiledModel = _saved["CompiledModel"]
+    from . import devices
+
+    devices.unregister_from_reference()
     _saved.clear()
 
 

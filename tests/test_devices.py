@@ -33,3 +33,69 @@ def test_calibration_measures_sane_constants():
     assert 20e12 < m.fp32_flops < 120e12
     assert 0.2e-6 < m.graph_launch_s < 10e-6 and 0.5e-6 < m.launch_s < 60e-6
     assert "flops_per_byte" in devices.report(m, devices.B200)
+
+
+# ---- the profile is wired into the reference (needs the reference) -----------------
+
+import pathlib  # noqa: E402
+import sys  # noqa: E402
+
+sys.path.insert(0, str(pathlib.Path(__file__).resolve().parent.parent / "oracle"))
+import ref as reference_copy  # noqa: E402
+
+needs_reference = pytest.mark.skipif(reference_copy.path() is None, reason="reference not present")
+
+
+def test_config_for_keeps_unknown_devices_on_the_defaults():
+    base = Config(pointwise_block=256)
+    assert devices.config_for("NVIDIA A40", base) is base
+    cfg = devices.config_for("NVIDIA B200", base)
+    assert cfg.pointwise_block == 256 and cfg.flops_per_byte == pytest.approx(devices.B200.flops_per_byte)
+
+
+@needs_reference
+def test_install_adds_the_b200_to_the_reference_device_table():
+    reference_copy.activate()
+    import mlc.devices as ref_devices
+    import mlc_compiler_b200 as mb
+
+    assert not any(k == "B200" for k, _ in ref_devices.TABLE)
+    mb.install()
+    try:
+        key, prof = ref_devices.TABLE[0]
+        assert key == "B200"
+        cfg = prof.to_config()
+        ours = devices.B200.to_config()
+        assert cfg.flops_per_byte == pytest.approx(ours.flops_per_byte)
+        assert cfg.launch_overhead_bytes == pytest.approx(ours.launch_overhead_bytes)
+        assert cfg.graph_launch_overhead_bytes == pytest.approx(ours.graph_launch_overhead_bytes)
+        mb.install()                                   # idempotent
+        assert sum(k == "B200" for k, _ in ref_devices.TABLE) == 1
+    finally:
+        mb.uninstall()
+    assert not any(k == "B200" for k, _ in ref_devices.TABLE)
+
+
+@needs_reference
+@pytest.mark.parametrize("name,batch,dtype", [("encoder-block", 1, torch.float32),
+                                              ("micro-layernorm", 8, torch.float16),
+                                              ("micro-softmax", 8, torch.float16),
+                                              ("micro-gelu", 8, torch.float16)])
+def test_b200_cost_constants_leave_the_shipped_schedules_unchanged(name, batch, dtype):
+    """The fusion and recompute decisions of the benchmark models are far from the
+    margin: pricing them for a B200 (10.4 FLOP/B, 3.6 MB per captured launch)
+    instead of the reference's A100 default (20 FLOP/B, 1.1 MB) yields the same
+    kernels, byte for byte -- which is why one set of shipped schedules serves both.
+    (``python -m mlc_compiler_b200.schedules.capture --check-profile`` runs the same
+    comparison over every shipped configuration.)"""
+    reference_copy.activate()
+    from mlc_compiler_b200 import capture_schedule, kir, models
+
+    model, inputs = models.build(name, batch, dtype=dtype)
+    a = capture_schedule(model, inputs, Config())
+    b = capture_schedule(model, inputs, devices.B200.to_config())
+    assert kir.dumps(a) == kir.dumps(b)
+    shipped = kir.dumps(__import__("mlc_compiler_b200").load_schedule(
+        models.schedule_name(name, batch, dtype)))
+    fresh = kir.loads(kir.dumps(b))
+    assert [k.summary() for k in fresh.kernels] == [k.summary() for k in kir.loads(shipped).kernels]

@@ -259,9 +259,11 @@ def test_auto_dependent_launch_keeps_the_faster_graph_and_the_same_answer():
     a = auto(*di).clone()
     assert auto.dependent_policy in ("chain", True)
     assert set(auto.policy_timings_ms) == {"chain", "True"}
-    chosen, other = auto.policy_timings_ms[str(auto.dependent_policy)], \
-        auto.policy_timings_ms["True" if auto.dependent_policy == "chain" else "chain"]
-    assert chosen <= other * 1.006
+    # structural, whatever the clock said: the recorded timings and the recorded choice
+    # obey the decision rule (library-edge launches are kept only if >= 0.5 % faster)
+    t = auto.policy_timings_ms
+    assert all(v > 0 for v in t.values())
+    assert (auto.dependent_policy is True) == (t["True"] < 0.995 * t["chain"])
     for policy in ("chain", True, False):
         fixed = CompiledModel(s, model, Config(dependent_launch=policy), dev)
         assert torch.equal(fixed(*di), a)
