@@ -94,6 +94,9 @@ class Config:
     #: turn ``mm`` + leading bias add into ``addmm`` (cuBLASLt bias epilogue).  Off by
     #: default: it changes how the matmul is dispatched and rounds once instead of twice
     bias_epilogue: bool = False
+    #: run independent pointwise kernels over the same iteration space as one launch
+    #: (BERT's q/k/v bias adds: 36 launches -> 12); bit-identical.  Off by default
+    fuse_siblings: bool = False
     #: streams the schedule is captured over.  1 reproduces the reference's single
     #: chain of graph nodes; more lets kernels with no dependency between them
     #: (physical byte ranges considered) run as parallel branches of the graph
@@ -113,6 +116,7 @@ class Config:
         produced it, on one stream."""
         return _replace(self, forward_into_copies=False, write_through_copies=False,
                         sequence_first=False, fold_embeddings=False, bias_epilogue=False,
+                        fuse_siblings=False,
                         graph_streams=1, dependent_launch="chain")
 
 

@@ -345,9 +345,19 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
     for s in k.steps:
         if isinstance(s, Reduce) or s.name in c.vec:
             note(s.expr, phase_of[s.name])
+    # An element output is stored in the first phase that has everything its
+    # expression reads (GPT-2's LayerNorm also emits the residual sum it normalises:
+    # stored as soon as it exists, that row stops occupying registers through both
+    # reductions).  An output that aliases an input keeps the last phase.
+    reduce_names = {s.name for s in k.steps if isinstance(s, Reduce)}
+    in_place = {a.buffer for a in k.inputs} & {a.buffer for a in k.outputs}
+    store_phase: dict[str, int] = {}
     for a in k.outputs:
         if a.name not in k.row_outputs:
-            note(k.out_expr[a.name], n_phases - 1)
+            ready = max([phase_of[nm] + (1 if nm in reduce_names else 0)
+                         for nm in kir.expr_refs(k.out_expr[a.name])] + [0])
+            store_phase[a.name] = n_phases - 1 if a.buffer in in_place else ready
+            note(k.out_expr[a.name], store_phase[a.name])
 
     # ---- operand access plans ---------------------------------------------
     acc_in: dict[int, Access] = {}
@@ -383,17 +393,21 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
                        f"({_col_off(a, 'c0')}), w{i}[q]);")
         pre.append("    }")
         c.lines[mark_ahead:mark_ahead] = pre
-    # registers the row itself occupies: the widest operand row in its register type,
-    # the packed words carried across the wait, and working room
-    words = lambda dt: max(1, kir.ITEMSIZE[dt] // 4) if dt not in kir.NARROW_FLOATS else 1   # noqa: E731
-    row_regs = NP * V * max([words(X.promoted_load_dtype(k.inputs[i].dtype)) for i in packed_in] or [1])
-    row_regs += sum(NP * max(1, V * kir.ITEMSIZE[k.inputs[i].dtype] // 4) for i in raw_in) + 16
-    c.lines[0] = _signature(k, name, geo.block, cfg, resident_ctas(geo, cfg, row_regs))
     for i in sorted(packed_in):
         if i in load_first:
             c.emit(f"    {X.REG_T[k.inputs[i].dtype]} v{i}[{NP}][{V}];  // {k.inputs[i].name}")
     kept = {nm for nm in c.vec if last_use.get(nm, -1) > phase_of[nm]}
     kept_decl: dict[str, str] = {}
+    # registers the row itself occupies: one row in its register type per value that
+    # is alive across the same reduction (at least one), the packed words carried
+    # across the wait, and working room
+    words = lambda dt: max(1, kir.ITEMSIZE[dt] // 4) if dt not in kir.NARROW_FLOATS else 1   # noqa: E731
+    width = max([words(X.promoted_load_dtype(k.inputs[i].dtype)) for i in packed_in] or [1])
+    live_rows = max([sum(1 for nm in kept if phase_of[nm] <= b < last_use[nm])
+                     for b in range(n_phases)] + [1])
+    row_regs = NP * V * width * live_rows
+    row_regs += sum(NP * max(1, V * kir.ITEMSIZE[k.inputs[i].dtype] // 4) for i in raw_in) + 16
+    c.lines[0] = _signature(k, name, geo.block, cfg, resident_ctas(geo, cfg, row_regs))
 
     def load_vals(in_loop_gather: bool) -> list[X.Val | None]:
         vals: list[X.Val | None] = []
@@ -437,8 +451,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
                 c.scalars[s.name] = X.Val(s.name, v.dtype, v.dim, False)
 
         vbinds = [s for s in phase_steps if isinstance(s, Bind) and s.name in c.vec]
-        stores = ([(i, a) for i, a in enumerate(k.outputs) if a.name not in k.row_outputs]
-                  if ph == n_phases - 1 else [])
+        stores = [(i, a) for i, a in enumerate(k.outputs) if store_phase.get(a.name) == ph]
         first_loads = sorted(i for i in acc_in if load_first.get(i) == ph and i in packed_in)
         gathers = sorted(i for i in acc_in if i not in packed_in
                          and load_first.get(i, 99) <= ph <= load_last.get(i, -1))

@@ -1078,6 +1078,93 @@ def read_through_copies(schedule: kir.Schedule, replan: bool = True) -> kir.Sche
     return _replanned(out) if replan else out
 
 
+# --------------------------------------------------------------------------
+# sibling pointwise kernels: one launch for several independent maps
+# --------------------------------------------------------------------------
+
+def _renumbered(e, slot_offset: int, prefix: str):
+    if isinstance(e, Load):
+        return Load(e.slot + slot_offset)
+    if isinstance(e, kir.Ref):
+        return kir.Ref(prefix + e.name)
+    if isinstance(e, Call):
+        return Call(e.fn, tuple(_renumbered(a, slot_offset, prefix) for a in e.args))
+    if isinstance(e, Cast):
+        return Cast(_renumbered(e.x, slot_offset, prefix), e.dtype)
+    return e
+
+
+def _merged(members: list) -> kir.PointwiseKernel:
+    inputs, outputs, body, out_expr, ops = [], [], [], {}, []
+    for j, m in enumerate(members):
+        off, pre = len(inputs), f"m{j}_"
+        inputs += list(m.inputs)
+        outputs += list(m.outputs)
+        body += [(pre + n, _renumbered(e, off, pre)) for n, e in m.body]
+        for a in m.outputs:
+            out_expr[a.name] = _renumbered(m.out_expr[a.name], off, pre)
+        ops += list(m.ops)
+    last = members[-1]
+    return kir.PointwiseKernel(last.name, last.space, inputs, outputs, body, out_expr, ops)
+
+
+def fuse_siblings(schedule: kir.Schedule, replan: bool = True, limit: int = 4) -> kir.Schedule:
+    """Run pointwise kernels that share an iteration space and do not depend on
+    each other as one launch (BERT's q, k and v bias adds: 36 launches -> 12).
+
+    Members keep their own operands, bodies and stores; the fused kernel is placed
+    where the last member was, which is legal when nothing between the first and
+    the last member touches a member's output or overwrites a member's input.
+    Values are unchanged.  Off by default: the members already run as parallel
+    branches of the graph, and joining them makes the fused launch wait for the
+    slowest producer (see ``Config.fuse_siblings`` for the measurement)."""
+    kernels = list(schedule.kernels)
+    finals = {v.buffer for v in schedule.outputs}
+    used: set[int] = set()
+    groups: list[list[int]] = []
+    for i, k in enumerate(kernels):
+        if i in used or not isinstance(k, kir.PointwiseKernel) or len(k.outputs) != 1:
+            continue
+        group = [i]
+        out_names = {a.name for a in k.outputs}
+        for j in range(i + 1, min(len(kernels), i + 12)):
+            c = kernels[j]
+            if len(group) >= limit:
+                break
+            if j in used or not isinstance(c, kir.PointwiseKernel) or len(c.outputs) != 1:
+                continue
+            if c.space != k.space or c.ops != k.ops or len(c.inputs) != len(k.inputs) \
+                    or [a.dtype for a in c.inputs + c.outputs] != [a.dtype for a in k.inputs + k.outputs] \
+                    or c.outputs[0].name in out_names or c.outputs[0].buffer in finals:
+                continue
+            members = [kernels[g] for g in group]
+            writes = {b for m in members for b in m.writes()}
+            reads = {b for m in members for b in m.reads()}
+            if (set(c.reads()) & writes) or (set(c.writes()) & (writes | reads)):
+                continue
+            # nothing in between may touch what the earlier members write, nor overwrite
+            # what they read: they now run at position j
+            between = [kernels[t] for t in range(group[0] + 1, j) if t not in group]
+            if any((set(b.reads()) | set(b.writes())) & writes or set(b.writes()) & reads
+                   for b in between):
+                continue
+            group.append(j)
+            out_names.add(c.outputs[0].name)
+        if len(group) > 1 and not any(kernels[g].outputs[0].buffer in finals for g in group):
+            groups.append(group)
+            used.update(group)
+    if not groups:
+        return schedule
+    for group in groups:
+        kernels[group[-1]] = _merged([kernels[g] for g in group])
+        for g in group[:-1]:
+            kernels[g] = None
+    out = kir.Schedule(name=schedule.name, kernels=[k for k in kernels if k is not None],
+                       buffers=schedule.buffers, inputs=schedule.inputs, outputs=schedule.outputs,
+                       params=schedule.params, plan=schedule.plan, meta=dict(schedule.meta))
+    return _replanned(out) if replan else out
+
+
 def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
     """Every rewrite ``cfg`` enables, in the order the executor applies them.
     Only arena-planned schedules are rewritten: the rewrites change live ranges
@@ -1097,4 +1184,6 @@ def prepare(schedule: kir.Schedule, cfg) -> kir.Schedule:
         work = write_through_copies(work)
     if getattr(cfg, "fold_embeddings", True):
         work = fold_embeddings(work)
+    if getattr(cfg, "fuse_siblings", False):
+        work = fuse_siblings(work)
     return work

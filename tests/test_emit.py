@@ -175,12 +175,42 @@ def test_tiny_modules_compile_for_sm_100a(stem, tmp_path):
 @needs_nvcc
 @pytest.mark.parametrize("name", ["bert-base_b1_s128_float16", "gpt2-small_b8_s128_bfloat16",
                                   "micro-gelu_b32_s128_float16", "micro-softmax_b8_s128_float16",
+                                  "micro-layernorm_b32_s128_float16",
+                                  "bert-base_b32_s128_float16", "gpt2-small_b32_s128_bfloat16",
                                   "bert-base-streamed_b1_s128_float16",
                                   "gpt2-small-streamed_b1_s128_float16"])
 def test_benchmark_modules_compile_for_sm_100a(name, tmp_path):
-    src = generate_module(load_schedule(name), Config()).source
+    """As the executor compiles them (rewrites applied); no kernel may spill, the
+    ones asked to stay resident for a single wave included."""
+    from mlc_compiler_b200 import rewrite
+
+    src = generate_module(rewrite.prepare(load_schedule(name), Config()), Config()).source
     log = B.nvcc_cubin(src, tmp_path / "m.cubin", verbose=True)
     assert not re.search(r"[1-9]\d* bytes spill stores", log)
+
+
+def test_outputs_are_stored_in_the_first_phase_that_has_their_value():
+    """GPT-2's LayerNorm kernels also emit the residual sum they normalise; it is
+    stored before the first reduction finishes instead of being carried to the end."""
+    from mlc_compiler_b200 import rewrite
+
+    s = rewrite.prepare(load_schedule("gpt2-small_b1_s128_float16"), Config())
+    k = next(k for k in s.generated() if isinstance(k, kir.ReductionKernel) and len(k.outputs) == 2)
+    text = generate_module(s, Config()).kernel_source(k.name)
+    first_reduce = text.index("mlcb_cta_reduce") if "mlcb_cta_reduce" in text else text.index("mlcb_group_reduce")
+    assert "out0 + out0_r" in text[:first_reduce] or "out1 + out1_r" in text[:first_reduce]
+    assert text.count("mlcb_store<__half, 8>") == 2
+
+
+def test_row_reductions_ask_for_single_wave_residency_when_the_row_fits():
+    from mlc_compiler_b200.emit.reduction import Geometry, resident_ctas
+
+    geo = Geometry(V=8, P=96, G=32, NP=3, block=128, rpb=4, grid=1024, masked=False)
+    assert resident_ctas(geo, Config(), 64) == 7           # 1024 CTAs / 148 SMs, 73 registers each
+    assert resident_ctas(geo, Config(), 100) == 5          # a fat row keeps its registers
+    assert resident_ctas(geo, Config(reduction_min_ctas=3), 64) == 3
+    small = Geometry(V=8, P=96, G=128, NP=1, block=128, rpb=1, grid=128, masked=True)
+    assert resident_ctas(small, Config(), 40) == 4         # nothing to gain: the floor
 
 
 @needs_nvcc
