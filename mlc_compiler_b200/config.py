@@ -56,8 +56,9 @@ class Config:
     #: load operands that no kernel of the schedule writes (weights, biases, masks)
     #: and do all index arithmetic *before* the grid-dependency wait, so that under
     #: programmatic dependent launch they overlap the predecessor's tail; the values
-    #: cross the wait as packed words (a quarter of the registers of the widened form)
-    hoist_stable_loads: bool = True
+    #: cross the wait as packed words (a quarter of the registers of the widened form).
+    #: True: launches that are resident all at once; "all": every launch; False: none
+    hoist_stable_loads: bool | str = True
     #: release the dependent launch right after the wait instead of after the
     #: kernel's own loads have been issued
     trigger_early: bool = False

@@ -67,6 +67,18 @@ def dependent_release(grid: int, block: int, cfg, indent: str = "    ") -> str |
     return None
 
 
+def loads_ahead_of_wait(grid: int, block: int, cfg) -> bool:
+    """Whether a launch fetches its parameters before the grid-dependency wait
+    (``Config.hoist_stable_loads``: False never, "all" always, True only when the
+    whole launch is resident at once).  CTAs of a later wave start long after the
+    predecessor has finished, so for them there is nothing to overlap and the
+    packed words held across the wait only cost registers: BERT-base at batch 32
+    runs 1.2 % slower with every launch hoisted, 2.5 % faster at batch 1 where all
+    launches are a fraction of a wave."""
+    mode = getattr(cfg, "hoist_stable_loads", True)
+    return bool(mode) and (mode == "all" or single_wave(grid, block))
+
+
 def pick_vector(operands, numel: int, cap_bytes: int = 16) -> int:
     smallest = min((kir.ITEMSIZE[a.dtype] for a in operands), default=4)
     v = max(1, cap_bytes // smallest)
@@ -143,11 +155,12 @@ def _emit_pointwise(k, cfg, buffers, name, stable=frozenset()) -> tuple[str, Lau
     early: list[str] = []   # loads of stable operands: issued before the wait
     after: list[str] = []   # everything that may read a predecessor's output
     need_idx = False
+    hoist = loads_ahead_of_wait(grid, block, cfg)
     for i, a in enumerate(k.inputs):
         acc = classify(a.index, "idx", V)
         st, rt = X.STORAGE_T[a.dtype], X.REG_T[a.dtype]
         vdt = X.promoted_load_dtype(a.dtype)
-        ahead = a.buffer in stable
+        ahead = hoist and a.buffer in stable
         if acc.mode == "bcast" and acc.width == V:
             (early if ahead else after).append(
                 f"    const {rt} v{i} = mlcb_load1<{st}>(in{i} + ({render_offset(a.index, at_i0)}));"

@@ -38,7 +38,8 @@ from ..kir import Bind, Reduce
 from . import expr as X
 from .indexing import (Access, check_bounds, classify, needs_64bit, pow2_ceil,
                        render_offset)
-from .pointwise import LaunchSpec, algorithmic_bytes, pick_vector, dependent_release, store_code
+from .pointwise import (LaunchSpec, algorithmic_bytes, dependent_release, loads_ahead_of_wait,
+                        pick_vector, store_code)
 
 _OP = {"sum": "mlcb_op_sum", "prod": "mlcb_op_prod", "max": "mlcb_op_max", "min": "mlcb_op_min"}
 
@@ -153,10 +154,11 @@ def varying_steps(k: kir.ReductionKernel) -> set[str]:
 class _Ctx:
     """Bookkeeping for one kernel emission."""
 
-    def __init__(self, k: kir.ReductionKernel, geo: Geometry, it: str, stable=frozenset()):
+    def __init__(self, k: kir.ReductionKernel, geo: Geometry, it: str, stable=frozenset(), cfg=None):
         self.k, self.geo, self.it = k, geo, it
         #: input slots whose buffer nothing writes: loadable before the wait
-        self.ahead = {i for i, a in enumerate(k.inputs) if a.buffer in stable and a.via is None}
+        self.ahead = {i for i, a in enumerate(k.inputs) if a.buffer in stable and a.via is None} \
+            if loads_ahead_of_wait(geo.grid, geo.block, cfg) else set()
         self.elide = X.store_only_casts([(s.name, s.expr) for s in k.steps if isinstance(s, Bind)],
                                         {n: e for n, e in k.out_expr.items()
                                          if n not in k.row_outputs},
@@ -305,7 +307,7 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
     extents = [k.n_rows * max(1, k.n_cols)] + [a.index.bounds()[1] + 1
                                                for a in k.inputs + k.outputs]
     it = "i64" if needs_64bit(*extents) else "int"
-    c = _Ctx(k, geo, it, stable)
+    c = _Ctx(k, geo, it, stable, cfg)
     reduces = k.reduces
     n_phases = len(reduces) + 1
 
@@ -371,13 +373,36 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
             acc_out[i] = ac if ac.mode == "contig" else Access("contig", 1)
 
     packed_in = {i for i, ac in acc_in.items() if ac.width > 1}
-    # stable operands read as whole packs: fetched before the wait as packed words
-    # (a quarter of the registers of the widened form), widened where first used
-    # (A prefetch.global.L1 of the same addresses instead -- no register held across
-    # the reductions -- was measured and is far slower on large launches: LayerNorm
-    # over [4096, 768] 8.1 us against 3.6 us.)
-    raw_in = sorted(i for i in packed_in if i in c.ahead and i in load_first
-                    and acc_in[i].mode == "contig" and acc_in[i].width == V)
+    kept = {nm for nm in c.vec if last_use.get(nm, -1) > phase_of[nm]}
+    kept_decl: dict[str, str] = {}
+    # registers the row itself occupies: one row in its register type per value that
+    # is alive across the same reduction (at least one) and working room
+    words = lambda dt: max(1, kir.ITEMSIZE[dt] // 4) if dt not in kir.NARROW_FLOATS else 1   # noqa: E731
+    width = max([words(X.promoted_load_dtype(k.inputs[i].dtype)) for i in packed_in] or [1])
+    live_rows = max([sum(1 for nm in kept if phase_of[nm] <= b < last_use[nm])
+                     for b in range(n_phases)] + [1])
+    row_regs = NP * V * width * live_rows + 16
+
+    # Stable operands read as whole packs are fetched before the wait as packed words
+    # (a quarter of the registers of the widened form) and widened where first used.
+    # The words are held across the reductions, so they are only taken while the launch
+    # still fits the machine in one wave with them: operands wanted last (LayerNorm's
+    # gain and bias, whose load would otherwise start after the reductions) go first,
+    # operands of the first phase -- needed together with the row itself -- last.
+    # (A prefetch.global.L1 of the same addresses instead, holding no register, was
+    # measured and is far slower on large launches: [4096, 768] 8.1 us against 3.6 us.)
+    candidates = sorted((i for i in packed_in if i in c.ahead and i in load_first
+                         and acc_in[i].mode == "contig" and acc_in[i].width == V),
+                        key=lambda i: (-load_first[i], i))
+    need = -(-geo.grid // SM_COUNT)
+    budget = 65536 // (geo.block * need) if need * geo.block <= 2048 else 255
+    raw_in: list[int] = []
+    for i in candidates:
+        cost = NP * max(1, V * kir.ITEMSIZE[k.inputs[i].dtype] // 4)
+        if row_regs + cost <= max(budget, 64) or getattr(cfg, "hoist_stable_loads", True) == "all":
+            raw_in.append(i)
+            row_regs += cost
+    raw_in.sort()
     if raw_in:
         pre = []
         for i in raw_in:
@@ -393,21 +418,10 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
                        f"({_col_off(a, 'c0')}), w{i}[q]);")
         pre.append("    }")
         c.lines[mark_ahead:mark_ahead] = pre
+    c.lines[0] = _signature(k, name, geo.block, cfg, resident_ctas(geo, cfg, row_regs))
     for i in sorted(packed_in):
         if i in load_first:
             c.emit(f"    {X.REG_T[k.inputs[i].dtype]} v{i}[{NP}][{V}];  // {k.inputs[i].name}")
-    kept = {nm for nm in c.vec if last_use.get(nm, -1) > phase_of[nm]}
-    kept_decl: dict[str, str] = {}
-    # registers the row itself occupies: one row in its register type per value that
-    # is alive across the same reduction (at least one), the packed words carried
-    # across the wait, and working room
-    words = lambda dt: max(1, kir.ITEMSIZE[dt] // 4) if dt not in kir.NARROW_FLOATS else 1   # noqa: E731
-    width = max([words(X.promoted_load_dtype(k.inputs[i].dtype)) for i in packed_in] or [1])
-    live_rows = max([sum(1 for nm in kept if phase_of[nm] <= b < last_use[nm])
-                     for b in range(n_phases)] + [1])
-    row_regs = NP * V * width * live_rows
-    row_regs += sum(NP * max(1, V * kir.ITEMSIZE[k.inputs[i].dtype] // 4) for i in raw_in) + 16
-    c.lines[0] = _signature(k, name, geo.block, cfg, resident_ctas(geo, cfg, row_regs))
 
     def load_vals(in_loop_gather: bool) -> list[X.Val | None]:
         vals: list[X.Val | None] = []
@@ -691,7 +705,7 @@ def _emit_streamed(k: kir.ReductionKernel, cfg, name: str, stable=frozenset()) -
     extents = [k.n_rows * max(1, k.n_cols)] + [a.index.bounds()[1] + 1
                                                for a in k.inputs + k.outputs]
     it = "i64" if needs_64bit(*extents) else "int"
-    c = _Ctx(k, geo, it, stable)
+    c = _Ctx(k, geo, it, stable, cfg)
     passes = plan_passes(k)
     reduces = k.reduces
     by_reduce = {r.name: p for p in passes for r in p.reduces}

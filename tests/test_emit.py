@@ -87,13 +87,17 @@ def test_only_parameters_nothing_writes_are_read_ahead_of_the_wait():
     precedes it."""
     from mlc_compiler_b200.emit.module import stable_buffers
 
-    for stem in ("bert-base_b1_s128_float16", "gpt2-small_b8_s128_bfloat16",
-                 "micro-layernorm_b32_s128_float16", "micro-softmax_b32_s128_float16",
-                 "micro-gelu_b32_s128_float16", "bert-base-streamed_b1_s128_float16"):
+    for stem, cfg in (("bert-base_b1_s128_float16", Config()),
+                      ("gpt2-small_b8_s128_bfloat16", Config()),
+                      ("micro-layernorm_b32_s128_float16", Config()),
+                      ("micro-softmax_b8_s128_float16", Config()),
+                      ("micro-softmax_b32_s128_float16", Config(hoist_stable_loads="all")),
+                      ("micro-gelu_b32_s128_float16", Config(hoist_stable_loads="all")),
+                      ("bert-base-streamed_b1_s128_float16", Config())):
         s = load_schedule(stem)
         stable = stable_buffers(s)
         assert stable <= set(s.params)
-        mod = generate_module(s, Config())
+        mod = generate_module(s, cfg)
         hoisted = 0
         for k in s.generated():
             head, tail = _before_and_after_the_wait(mod.kernel_source(k.name))
@@ -106,6 +110,34 @@ def test_only_parameters_nothing_writes_are_read_ahead_of_the_wait():
                 if a.buffer not in stable:
                     assert f"in{i} +" not in head and f"in{i} +" in tail
         assert hoisted >= 1, stem
+
+
+def test_launches_of_several_waves_keep_their_loads_behind_the_wait():
+    """CTAs of a later wave start after the predecessor has finished: nothing to
+    overlap, and words held across the wait would only cost registers."""
+    for stem in ("micro-gelu_b32_s128_float16", "micro-softmax_b32_s128_float16"):
+        s = load_schedule(stem)
+        text = generate_module(s, Config()).kernel_source(s.generated()[0].name)
+        head, _ = _before_and_after_the_wait(text)
+        assert "mlcb_load" not in head
+        assert "mlcb_load_raw" in generate_module(s, Config(hoist_stable_loads="all")).source
+
+
+def test_hoisting_never_costs_a_row_reduction_its_single_wave():
+    """bias + residual + LayerNorm over [4096, 768]: gain and bias (wanted after the
+    reductions) cross the wait, the projection bias (needed with the row itself) does
+    not, because with it the 1024-CTA launch would no longer fit in one wave."""
+    from mlc_compiler_b200 import rewrite
+
+    s = rewrite.prepare(load_schedule("bert-base_b32_s128_float16"), Config())
+    k = next(k for k in s.generated() if isinstance(k, kir.ReductionKernel) and len(k.inputs) == 5)
+    text = generate_module(s, Config()).kernel_source(k.name)
+    head, tail = _before_and_after_the_wait(text)
+    assert head.count("mlcb_load_raw<__half, 8>") == 2 and "__launch_bounds__(128, 7)" in text
+    one = rewrite.prepare(load_schedule("bert-base_b1_s128_float16"), Config())
+    k1 = next(k for k in one.generated() if isinstance(k, kir.ReductionKernel) and len(k.inputs) == 5)
+    head1, _ = _before_and_after_the_wait(generate_module(one, Config()).kernel_source(k1.name))
+    assert head1.count("mlcb_load_raw<__half, 8>") == 3          # a fraction of a wave: all three
 
 
 def test_layernorm_weights_cross_the_wait_as_packed_words():
