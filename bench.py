@@ -69,8 +69,8 @@ STATIC_CONFIG = {"workload": WORKLOAD, "accumulate": "f32", "batch": 1, "seq_len
 #: the figure, so it can be below the algorithmic bytes.
 NCU_TRAFFIC: dict[str, int] = {
     "mlcb_red_4357894e362b": 6302720,              # LayerNorm [4096, 768]: 6,302,720 read + 0 written
-    "mlcb_red_7cbf8dea7dc8": 12623872,             # causal softmax [49152, 128]: 12,623,872 + 0
-    "mlcb_pw_ad8b0a2a3110": 50348800 + 1605888,    # bias+GELU+residual [4096, 3072]
+    "mlcb_red_080b5360d44a": 12623360,             # causal softmax [49152, 128]: 12,623,360 + 0
+    "mlcb_pw_9dd2f6a63b0f": 50347008 + 1423104,    # bias+GELU+residual [4096, 3072]
 }
 
 
@@ -430,7 +430,7 @@ def run_reference(args) -> int:
 # same-method comparison with the reference's Triton build (bench-only)
 # --------------------------------------------------------------------------
 
-def same_method_comparison(dev, rounds: int = 5) -> dict:
+def same_method_comparison(dev, rounds: int = 5, batches=(1,)) -> dict:
     """Compile one model object three ways through the reference's public
     ``mlc.compile`` -- its stock Triton backend; this backend under the reference's
     own executor (``install()``); this backend with this package's executor
@@ -467,10 +467,10 @@ def same_method_comparison(dev, rounds: int = 5) -> dict:
             ts.append(s.elapsed_time(e))
         return statistics.median(ts)
 
-    for name in ("bert-base", "gpt2-small"):
-        key = name.replace("-", "_") + "_b1"
+    for name, batch in [(n, b) for n in ("bert-base", "gpt2-small") for b in batches]:
+        key = name.replace("-", "_") + f"_b{batch}"
         try:
-            model, inputs = models.build(name, 1, dtype=torch.float16)
+            model, inputs = models.build(name, batch, dtype=torch.float16)
             model = model.to(dev)
             inputs = tuple(t.to(dev) for t in inputs)
             mb.uninstall()
@@ -597,7 +597,8 @@ def run_ours(args) -> int:
         group.close()
         return 0
     if args.section == "same-method":
-        print(json.dumps(same_method_comparison(dev)))
+        batches = tuple(int(b) for b in args.batches.split(","))
+        print(json.dumps(same_method_comparison(dev, batches=batches)))
         return 0
     if args.section == "compare":
         # this backend alone, timed as the reference's harness does (mlc/bench/runner.py:84-112):
@@ -768,6 +769,7 @@ def main() -> int:
     ap.add_argument("--dtype", default="float16")
     ap.add_argument("--only", default=None, metavar="KERNEL:BATCH",
                     help="with --section micro: one row, e.g. micro-gelu:8")
+    ap.add_argument("--batches", default="1", help="with --section same-method: e.g. 1,8,32")
     ap.add_argument("--branches", type=int, default=4,
                     help="parallel graph branches of the extra batch-32 microbenchmark figure (0 = skip)")
     ap.add_argument("--cfg", action="append", default=[], metavar="KEY=VALUE",
