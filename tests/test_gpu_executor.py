@@ -292,3 +292,31 @@ def test_sequence_first_attention_storage_gives_the_same_answer(name, batch):
     # same library calls on the same values; rows reach the output projection in
     # another order, which may change cuBLAS's tiling but not what is computed
     assert (a - b).abs().max().item() <= 1e-2 * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,batch", [("bert-base", 1), ("bert-base", 8), ("gpt2-small", 4)])
+def test_emitter_and_rewrite_options_change_timing_only(name, batch):
+    """Where parameters are loaded relative to the grid-dependency wait, where an
+    output row is stored, and whether sibling bias adds share a launch are all
+    arrangements of the same arithmetic: outputs are bit-identical."""
+    import torch
+    from mlc_compiler_b200 import Config, models
+    from mlc_compiler_b200.executor import CompiledModel
+    from mlc_compiler_b200.frontend import load_schedule
+
+    dev = torch.device("cuda", 0)
+    s = load_schedule(models.schedule_name(name, batch, torch.float16))
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    di = [t.to(dev) for t in inputs]
+    base = CompiledModel(s, model, Config(), dev)
+    base(*di)
+    want = base(*di).clone()
+    for kw in ({"hoist_stable_loads": False}, {"hoist_stable_loads": "all"}, {"fuse_siblings": True},
+               {"trigger_early": True}, {"reduction_min_ctas": 2}):
+        other = CompiledModel(s, model, Config(**kw), dev)
+        other(*di)
+        assert torch.equal(other(*di), want), kw
+    fused = CompiledModel(s, model, Config(fuse_siblings=True), dev)
+    if name == "bert-base":
+        assert len(fused.executed_schedule) == len(base.executed_schedule) - 24

@@ -390,3 +390,42 @@ def test_pure_copy_does_not_see_through_a_narrowing_round_trip():
     assert rewrite._pure_copy(copy("float16", "float32"))        # widening and back: identity
     assert rewrite._pure_copy(copy("float32", "float32"))
     assert not rewrite._pure_copy(copy("float64", "float32"))    # rounds to 24 bits on the way
+
+
+# ---- sibling pointwise kernels as one launch (opt-in) -----------------------------
+
+@pytest.mark.parametrize("name,batch", [("bert-base", 1), ("bert-base", 4)])
+def test_sibling_fusion_merges_the_three_projection_bias_adds(name, batch):
+    s = load_schedule(models.schedule_name(name, batch, torch.float16))
+    base = rewrite.prepare(s, Config())
+    fused = rewrite.prepare(s, Config(fuse_siblings=True))
+    assert len(base) - len(fused) == 24                         # 36 adds -> 12 launches
+    merged = [k for k in fused.generated() if isinstance(k, kir.PointwiseKernel) and len(k.outputs) == 3]
+    assert len(merged) == 12 and all(k.ops == ["add"] * 3 and len(k.inputs) == 6 for k in merged)
+    # the fused launch sits where its last member was: after all three producers
+    order = {k.name: i for i, k in enumerate(fused.kernels)}
+    for m in merged:
+        producers = [k for k in fused.kernels if set(k.writes()) & set(m.reads())]
+        assert all(order[p.name] < order[m.name] for p in producers)
+    model, inputs = models.build(name, batch, dtype=torch.float16)
+    a, _ = oracle.run_schedule(base, model, inputs)
+    b, _ = oracle.run_schedule(fused, model, inputs)
+    assert torch.equal(a, b)
+
+
+def test_sibling_fusion_refuses_members_that_depend_on_each_other():
+    n = 64
+    ax = _ax(n, (n, 1, 1))
+
+    def add_one(name, src, dst):
+        return kir.PointwiseKernel(name, (n,), [kir.Operand(src, src, "float32", ax)],
+                                   [kir.Operand(dst, dst, "float32", ax)],
+                                   [("t0", kir.Call("add", (kir.Load(0), kir.Const(1.0))))],
+                                   {dst: kir.Ref("t0")}, ["add"])
+
+    bufs = {b: kir.BufferSpec(b, (n,), "float32", kind) for b, kind in
+            (("x", "input"), ("y", "intermediate"), ("z", "intermediate"), ("w", "output"))}
+    chain = kir.Schedule("chain", [add_one("k0", "x", "y"), add_one("k1", "y", "z"), add_one("k2", "z", "w")],
+                         bufs, inputs=[kir.View("x", "x", (n,), (1,), 0)],
+                         outputs=[kir.View("w", "w", (n,), (1,), 0)])
+    assert rewrite.fuse_siblings(chain, replan=False) is chain
