@@ -3,8 +3,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one forward of the compiled schedule.  Rank 0 prints ONE JSON line,
-kept short; the long per-kernel tables go to ``gpurun_out/bench_details.json``
-when that directory can be written.
+kept short; ``--details FILE`` additionally writes the long per-kernel tables
+(grid, block, registers and buffer sets of every microbenchmark cell, every
+in-model function, the replica rows, the same-method comparison) as JSON.
 
 * ``value`` / ``ms_per_step``: latency of one graph replay with the inputs already
   in device memory, per-step CUDA events, L2 flushed (a 256 MiB write) between
@@ -533,7 +534,7 @@ def replica_rows(group, dev, steps: int, flush, cfg_kw, combos=None) -> list[dic
             if i >= 2:
                 e2e.append(wall)
         e2e_ms = statistics.mean(e2e)
-        rows.append({"model": name, "dtype": str(dt).split(".")[-1].replace("float", "f").replace("bf", "bf"),
+        rows.append({"model": name, "dtype": str(dt).split(".")[-1].replace("float", "f"),
                      "per_gpu_batch": per_gpu, "seq_per_s": round(thr["seq_per_s"], 1),
                      "ms_slowest": round(thr["ms_per_forward"], 4),
                      "e2e_seq_per_s": round(32 / (e2e_ms / 1e3), 1), "e2e_ms": round(e2e_ms, 3),
@@ -550,12 +551,14 @@ def barrier(group) -> None:
     torch.cuda.synchronize()
 
 
-def _write_details(details: dict) -> str | None:
-    out = ROOT / "gpurun_out"
+def _write_details(details: dict, path: str | None) -> str | None:
+    if not path:
+        return None
+    out = pathlib.Path(path)
     try:
-        out.mkdir(exist_ok=True)
-        (out / "bench_details.json").write_text(json.dumps(details, indent=1))
-        return "gpurun_out/bench_details.json"
+        out.parent.mkdir(parents=True, exist_ok=True)
+        out.write_text(json.dumps(details, indent=1))
+        return str(path)
     except OSError:
         return None
 
@@ -743,7 +746,9 @@ def run_ours(args) -> int:
             note = sm.get("unavailable") or bert.get("unavailable") or gpt.get("unavailable")
             if note:
                 config["triton_note"] = note
-        line["details"] = _write_details(details)
+        written = _write_details(details, args.details)
+        if written:
+            line["details"] = written
     barrier(group)
     if rank == 0:
         print(json.dumps(line, separators=(",", ":")))
@@ -769,6 +774,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="float16")
     ap.add_argument("--only", default=None, metavar="KERNEL:BATCH",
                     help="with --section micro: one row, e.g. micro-gelu:8")
+    ap.add_argument("--details", default=None, metavar="FILE",
+                    help="also write the long per-kernel tables to this JSON file")
     ap.add_argument("--batches", default="1", help="with --section same-method: e.g. 1,8,32")
     ap.add_argument("--branches", type=int, default=4,
                     help="parallel graph branches of the extra batch-32 microbenchmark figure (0 = skip)")
