@@ -1,14 +1,15 @@
 """Test infrastructure: the reference itself, installed beside the CPU oracle.
 
-The reference compiler is pure Python (package ``mlc`` plus the model zoo its
-tests use, ``tests/models.py``).  :func:`install` copies those files from a
-checkout of the reference into ``oracle/_ref/`` -- a directory that is never
-committed -- so that machines without the checkout can still run the
-reference's own code:
+The reference compiler is pure Python (package ``mlc`` plus its ``tests/``).
+:func:`install` copies those files from a checkout of the reference into
+``oracle/_ref/`` -- a directory that is never committed -- so that machines
+without the checkout can still run the reference's own code:
 
 * as the checker of the drop-in boundary (``tests/test_gpu_reference.py`` drives
   ``mlc.compile`` with this backend installed against the reference's torch
-  backend, ``mlc/codegen/torch_backend.py:100-248``),
+  backend, ``mlc/codegen/torch_backend.py:100-248``;
+  ``tests/test_gpu_reference_suite.py`` runs the reference's own test files on
+  the GPU with this backend installed),
 * as the timed CPU baseline (``bench.py --impl reference`` and the
   ``cpu_baseline`` leg), and
 * as the comparison arm that runs the reference's stock Triton build
@@ -30,8 +31,9 @@ import sys
 
 HERE = pathlib.Path(__file__).resolve().parent
 DEST = HERE / "_ref"
-#: what the checker needs of a checkout: the package and the test model zoo
-PIECES = ("mlc", "tests/models.py")
+#: what the checker needs of a checkout: the package and its test suite (model zoo
+#: included), which ``tests/test_gpu_reference_suite.py`` runs on the GPU unmodified
+PIECES = ("mlc", "tests")
 
 
 def default_source() -> pathlib.Path:
