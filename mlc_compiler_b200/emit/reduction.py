@@ -571,8 +571,8 @@ def _emit_persistent(k: kir.ReductionKernel, cfg, name: str, stable=frozenset())
         if red is not None:
             _finish_reduce(c, red, acc_dt, rdt, reduces.index(red))
         if ph == 0 and not getattr(cfg, "trigger_early", False) \
-                and dependent_release(geo.grid, geo.block, cfg):
-            c.emit(dependent_release(geo.grid, geo.block, cfg))
+                and dependent_release(geo.grid, geo.block, cfg, registers=row_regs):
+            c.emit(dependent_release(geo.grid, geo.block, cfg, registers=row_regs))
 
     _row_stores(c, loads)
     c.emit("}")
