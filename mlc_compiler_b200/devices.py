@@ -102,6 +102,25 @@ def register_with_reference() -> bool:
     return True
 
 
+def use_cuda_probe_in_reference() -> bool:
+    """Give the reference's calibration (``mlc/bench/calibrate.py:141-168``) this
+    package's CUDA fp32 probe in place of its Triton kernel (``:46-59,119-138``),
+    so that ``python -m mlc.bench --calibrate`` measures all four constants on a
+    machine without Triton.  Separate from :func:`register_with_reference`
+    because importing ``mlc.bench.calibrate`` imports Triton where it is present,
+    which ``install()`` must not do.  Returns False when the reference is absent."""
+    import importlib
+
+    try:
+        cal = importlib.import_module("mlc.bench.calibrate")
+    except ImportError:
+        return False
+    if not hasattr(cal, "_mlcb_saved_fp32_probe"):
+        cal._mlcb_saved_fp32_probe = cal.measure_fp32_throughput
+    cal.measure_fp32_throughput = measure_fp32_throughput
+    return True
+
+
 def unregister_from_reference() -> None:
     try:
         import importlib
@@ -110,6 +129,12 @@ def unregister_from_reference() -> None:
     except ImportError:
         return
     ref.TABLE[:] = [(k, p) for k, p in ref.TABLE if k != "B200"]
+    import sys
+
+    cal = sys.modules.get("mlc.bench.calibrate")
+    if cal is not None and hasattr(cal, "_mlcb_saved_fp32_probe"):
+        cal.measure_fp32_throughput = cal._mlcb_saved_fp32_probe
+        del cal._mlcb_saved_fp32_probe
 
 
 # --------------------------------------------------------------------------
@@ -135,6 +160,47 @@ extern "C" __global__ void __launch_bounds__(256) mlcb_probe_fma(float* out, int
     if (x0 + x1 + x2 + x3 == -1.0f) out[0] = x0;
 }
 """
+
+
+def measure_fp32_throughput(device="cuda", n: int = 1 << 20, chain: int = 512) -> float:
+    """fp32 operations per second of pointwise code on ``device``: ``n`` threads
+    each run four independent chains of ``chain`` fused multiply-adds.  Same
+    signature and meaning as the reference's probe
+    (``mlc/bench/calibrate.py:119-138``), which is a Triton kernel; this one is
+    CUDA C++ compiled and launched through the C ABI, and ``install()`` puts it in
+    the reference's place."""
+    import ctypes
+
+    import torch
+
+    from .runtime import LoadedModule, _check, compile_source
+
+    dev = torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(index):
+        mod = LoadedModule(compile_source(_PROBES), index)
+        buf = torch.zeros(16, device=torch.device("cuda", index))
+        iters = max(1, int(chain) * 4)
+        grid = max(1, int(n) // 256)
+        arr = (ctypes.c_uint64 * 2)(buf.data_ptr(), iters)
+        kernel = mod.kernel("mlcb_probe_fma")
+
+        def launch():
+            stream = torch.cuda.current_stream(index).cuda_stream
+            _check(mod.lib, mod.lib.mlcb_launch(kernel, grid, 256, 0, arr, 2, stream, 0), "mlcb_probe_fma")
+
+        for _ in range(3):
+            launch()
+        torch.cuda.synchronize(index)
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        s_.record()
+        for _ in range(reps):
+            launch()
+        e_.record()
+        torch.cuda.synchronize(index)
+        seconds = s_.elapsed_time(e_) * 1e-3 / reps
+    return grid * 256 * 4 * 2 * iters / seconds
 
 
 def calibrate(device="cuda", quick: bool = False) -> DeviceProfile:

@@ -99,3 +99,40 @@ def test_b200_cost_constants_leave_the_shipped_schedules_unchanged(name, batch, 
         models.schedule_name(name, batch, dtype)))
     fresh = kir.loads(kir.dumps(b))
     assert [k.summary() for k in fresh.kernels] == [k.summary() for k in kir.loads(shipped).kernels]
+
+
+@needs_reference
+def test_cuda_probe_takes_the_place_of_the_reference_triton_probe():
+    reference_copy.activate()
+    import mlc_compiler_b200 as mb
+
+    assert devices.use_cuda_probe_in_reference()
+    import mlc.bench.calibrate as cal
+
+    assert cal.measure_fp32_throughput is devices.measure_fp32_throughput
+    mb.install()
+    mb.uninstall()                                   # restores the reference's own probe
+    assert cal.measure_fp32_throughput is not devices.measure_fp32_throughput
+
+
+@pytest.mark.gpu
+@needs_reference
+def test_reference_calibration_runs_on_the_cuda_probe():
+    """``mlc.bench.calibrate.calibrate`` -- the reference's own routine -- with its
+    fp32 probe replaced: all four constants measured, none taken from the table."""
+    reference_copy.activate()
+    import mlc_compiler_b200 as mb
+
+    mb.install()
+    try:
+        assert devices.use_cuda_probe_in_reference()
+        import mlc.bench.calibrate as cal
+
+        prof = cal.calibrate("cuda:0", quick=True)
+        assert prof.source == "measured"
+        assert 20e12 < prof.fp32_flops < 120e12
+        assert 2e12 < prof.bandwidth < 9e12
+        cfg = prof.to_config()
+        assert 3 < cfg.flops_per_byte < 40
+    finally:
+        mb.uninstall()
