@@ -22,6 +22,13 @@ FLOATS = ("float32", "float16", "bfloat16")
 
 class Gen:
     def __init__(self, seed: int):
+        #: a second stream decides which inputs are parameters and which reductions get
+        #: a second element output, so that the kernels themselves stay what they were
+        import random as _random
+        self.side = _random.Random(seed * 7919 + 13)
+        #: input buffers declared as parameters (nothing writes them): the emitter loads
+        #: those ahead of the grid-dependency wait
+        self.params: list[str] = []
         self.r = random.Random(seed)
         self.g = torch.Generator().manual_seed(seed)
 
@@ -128,7 +135,10 @@ class Gen:
             idt = dt if r.random() < 0.8 else r.choice(FLOATS + ("int64",))
             strides, numel, base = self.view(space)
             bname = f"{name}_in{i}"
-            specs[bname] = kir.BufferSpec(bname, (numel,), idt, "input")
+            is_param = self.side.random() < 0.4
+            specs[bname] = kir.BufferSpec(bname, (numel,), idt, "param" if is_param else "input")
+            if is_param:
+                self.params.append(bname)
             buffers[bname] = self.tensor(numel, idt)
             m = self.index_map([("idx", list(zip(space, strides)))], strides, base)
             inputs.append(kir.Operand(bname, bname, idt, m))
@@ -178,7 +188,10 @@ class Gen:
             else:
                 numel = rows
                 m = self.index_map([("row", [(rows, 1)]), ("col", [(cols, 0)])], None, 0)
-            specs[bname] = kir.BufferSpec(bname, (numel,), dt, "input")
+            is_param = self.side.random() < 0.5
+            specs[bname] = kir.BufferSpec(bname, (numel,), dt, "param" if is_param else "input")
+            if is_param:
+                self.params.append(bname)
             buffers[bname] = self.tensor(numel, dt)
             inputs.append(kir.Operand(bname, bname, dt, m))
         leaves = [kir.Load(i) for i in range(len(inputs))]
@@ -209,6 +222,16 @@ class Gen:
         outs = [kir.Operand(elem, elem, dt, self.index_map(
             [("row", [(rows, cols)]), ("col", [(cols, 1)])], None, 0))]
         out_expr = {elem: kir.Ref("t9")}
+        if not streamed and self.side.random() < 0.4:
+            # a second element output whose value exists before the first reduction
+            # (the residual sum a LayerNorm also emits): stored in the first phase
+            early = f"{name}_out2"
+            specs[early] = kir.BufferSpec(early, (rows * cols,), dt, "output")
+            buffers[early] = torch.zeros(rows * cols, dtype=kir.torch_dtype(dt))
+            outs.append(kir.Operand(early, early, dt, self.index_map(
+                [("row", [(rows, cols)]), ("col", [(cols, 1)])], None, 0)))
+            steps.insert(1, kir.Bind("t0c", kir.Cast(kir.Ref("t0"), dt)))
+            out_expr[early] = kir.Ref("t0c")
         row_outputs = set()
         if r.random() < 0.5:
             rname = f"{name}_out1"

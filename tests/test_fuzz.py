@@ -30,7 +30,7 @@ def corpus(seed: int = 2024):
     for i in range(N_REDUCTION):
         k, s, b = g.reduction(f"r{i}", streamed=(i % 3 == 2))
         kernels.append(k), specs.update(s), buffers.update(b)
-    sched = kir.Schedule("fuzz", kernels, specs)
+    sched = kir.Schedule("fuzz", kernels, specs, params={b: b for b in g.params})
     return sched, buffers
 
 
@@ -39,6 +39,17 @@ def test_corpus_is_accepted_by_the_oracle_and_the_emitter(seed):
     sched, buffers = corpus(seed)
     mod = generate_module(sched, Config())
     assert len(mod.launch) == N_POINTWISE + N_REDUCTION
+    # the corpus reaches the paths that depend on what a schedule declares: parameters
+    # read ahead of the grid-dependency wait (packed and per-row scalar), and element
+    # outputs stored before the first reduction
+    assert len(sched.params) >= 30
+    assert mod.source.count("mlcb_load_raw<") >= 10
+    early = [k for k in sched.kernels if isinstance(k, kir.ReductionKernel)
+             and sum(a.name not in k.row_outputs for a in k.outputs) == 2]
+    assert len(early) >= 3
+    for k in early:
+        text = mod.kernel_source(k.name)
+        assert text.index("out1 + out1_r") < text.index("_reduce<")
     for k in sched.kernels:
         oracle.run_kernel(k, buffers)
         for a in k.outputs:
