@@ -347,6 +347,9 @@ class CompiledModel:
         return buffers
 
     def forward(self, *inputs: torch.Tensor):
+        if torch.cuda.current_device() != self.device.index:
+            with torch.cuda.device(self.device):
+                return self.forward(*inputs)
         if self._exec.plan.mode == "eager":
             return self._collect(self._run_eager(inputs))
         buffers = self._resident_buffers(inputs)
